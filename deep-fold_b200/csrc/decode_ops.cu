@@ -1,0 +1,505 @@
+// Small decode-step kernels for sm_100a: RMSNorm, RoPE + KV write, GQA decode
+// attention over the valid KV prefix, packed-embedding row decode and the
+// greedy pick + commit.
+//
+// Attention differs from the reference's launch shape on purpose: one CTA owns a
+// (kv head, sequence split) pair and serves every query head of that kv head, so
+// a cache row is read once per group instead of once per query head.
+
+#include "nf4_common.cuh"
+
+namespace chr {
+namespace {
+
+// ----------------------------------------------------------------------------
+// RMSNorm  (reference: gpu/nf4/nf4_gemv.cu:729-751)
+// ----------------------------------------------------------------------------
+constexpr int kRmsThreads = 256;
+
+__global__ void __launch_bounds__(kRmsThreads) rms_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                         const __nv_bfloat16 *__restrict__ w,
+                                                         __nv_bfloat16 *__restrict__ y, int n,
+                                                         float eps) {
+  __shared__ float red[kRmsThreads / 32];
+  const int tid = threadIdx.x;
+  float acc = 0.f;
+  for (int i = tid; i < n; i += kRmsThreads) {
+    const float v = __bfloat162float(x[i]);
+    acc += v * v;
+  }
+  acc = warp_sum_xor(acc);
+  if ((tid & 31) == 0) red[tid >> 5] = acc;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kRmsThreads / 32; ++i) tot += red[i];
+  const float s = rsqrtf(tot / static_cast<float>(n) + eps);
+  for (int i = tid; i < n; i += kRmsThreads) {
+    y[i] = __float2bfloat16(__bfloat162float(w[i]) * __bfloat162float(x[i]) * s);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Standalone RoPE + cache write  (reference: gpu/nf4/nf4_gemv.cu:497-537)
+// ----------------------------------------------------------------------------
+__global__ void rope_kv_kernel(__nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__restrict__ k,
+                               const __nv_bfloat16 *__restrict__ v,
+                               __nv_bfloat16 *__restrict__ k_cache,
+                               __nv_bfloat16 *__restrict__ v_cache,
+                               const __nv_bfloat16 *__restrict__ cos,
+                               const __nv_bfloat16 *__restrict__ sin,
+                               const int64_t *__restrict__ position, int n_q, int n_kv, int hd,
+                               int max_seq) {
+  const long long pos = *position;
+  if (pos < 0 || pos >= max_seq) return;
+  const int head = blockIdx.x;
+  const bool is_q = head < n_q;
+  __nv_bfloat16 *vec = is_q ? q + static_cast<size_t>(head) * hd
+                            : k + static_cast<size_t>(head - n_q) * hd;
+  const __nv_bfloat16 *c = cos + static_cast<size_t>(pos) * hd;
+  const __nv_bfloat16 *s = sin + static_cast<size_t>(pos) * hd;
+  const int half = hd >> 1;
+  for (int d = threadIdx.x; d < half; d += blockDim.x) {
+    const float lo = __bfloat162float(vec[d]);
+    const float hi = __bfloat162float(vec[d + half]);
+    vec[d] = __float2bfloat16(lo * __bfloat162float(c[d]) + (-hi) * __bfloat162float(s[d]));
+    vec[d + half] =
+        __float2bfloat16(hi * __bfloat162float(c[d + half]) + lo * __bfloat162float(s[d + half]));
+  }
+  if (!is_q) {
+    __syncthreads();
+    const size_t off = (static_cast<size_t>(pos) * n_kv + (head - n_q)) * hd;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+      k_cache[off + d] = vec[d];
+      v_cache[off + d] = v[static_cast<size_t>(head - n_q) * hd + d];
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// GQA decode attention  (reference: gpu/nf4/nf4_gemv.cu:558-727)
+// ----------------------------------------------------------------------------
+constexpr int kAttnWarps = 4;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr float kNegInit = -1.0e30f;
+
+// P: bf16 pairs per lane (hd <= 64*P). H: query heads served by one CTA.
+template <int P, int H>
+__global__ void __launch_bounds__(kAttnThreads)
+attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_cache,
+                  const __nv_bfloat16 *v_cache, float *__restrict__ m_s, float *__restrict__ l_s,
+                  float *__restrict__ o_s, const int32_t *__restrict__ valid_len,
+                  const __nv_bfloat16 *__restrict__ k_act, const __nv_bfloat16 *__restrict__ v_act,
+                  const __nv_bfloat16 *__restrict__ cos, const __nv_bfloat16 *__restrict__ sin,
+                  const int64_t *__restrict__ position, int n_q, int n_kv, int hd, int n_split,
+                  int max_seq, float scale) {
+  __shared__ float qrot[H][64 * P];
+  __shared__ float krot[64 * P];
+  __shared__ float vcur[64 * P];
+  __shared__ float sm_m[kAttnWarps][H];
+  __shared__ float sm_l[kAttnWarps][H];
+  __shared__ float sm_o[kAttnWarps][H][64 * P];
+
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int n_rep = n_q / n_kv;
+  const int h_first = kvh * n_rep + blockIdx.z * H;  // first query head of this CTA
+  const int nh = min(H, n_rep - static_cast<int>(blockIdx.z) * H);
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int half = hd >> 1;
+
+  int vl = *valid_len;
+  vl = vl < 0 ? 0 : (vl > max_seq ? max_seq : vl);
+
+  long long pos = -1;
+  bool fuse_kv = false;
+  const bool have_rope = cos != nullptr && sin != nullptr && position != nullptr;
+  if (have_rope) {
+    pos = *position;
+    if (pos < 0 || pos >= max_seq) pos = -1;
+  }
+  if (pos >= 0) {
+    const __nv_bfloat16 *c = cos + static_cast<size_t>(pos) * hd;
+    const __nv_bfloat16 *s = sin + static_cast<size_t>(pos) * hd;
+    for (int i = tid; i < nh * half; i += kAttnThreads) {
+      const int h = i / half;
+      const int d = i - h * half;
+      const __nv_bfloat16 *qh = q + static_cast<size_t>(h_first + h) * hd;
+      const float lo = __bfloat162float(qh[d]);
+      const float hi = __bfloat162float(qh[d + half]);
+      qrot[h][d] = lo * __bfloat162float(c[d]) + (-hi) * __bfloat162float(s[d]);
+      qrot[h][d + half] = hi * __bfloat162float(c[d + half]) + lo * __bfloat162float(s[d + half]);
+    }
+    if (k_act != nullptr && v_act != nullptr) {
+      fuse_kv = true;
+      const __nv_bfloat16 *ka = k_act + static_cast<size_t>(kvh) * hd;
+      const __nv_bfloat16 *va = v_act + static_cast<size_t>(kvh) * hd;
+      for (int d = tid; d < half; d += kAttnThreads) {
+        const float lo = __bfloat162float(ka[d]);
+        const float hi = __bfloat162float(ka[d + half]);
+        krot[d] = lo * __bfloat162float(c[d]) + (-hi) * __bfloat162float(s[d]);
+        krot[d + half] = hi * __bfloat162float(c[d + half]) + lo * __bfloat162float(s[d + half]);
+      }
+      for (int d = tid; d < hd; d += kAttnThreads) vcur[d] = __bfloat162float(va[d]);
+    }
+  } else {
+    for (int i = tid; i < nh * hd; i += kAttnThreads) {
+      const int h = i / hd;
+      const int d = i - h * hd;
+      qrot[h][d] = __bfloat162float(q[static_cast<size_t>(h_first + h) * hd + d]);
+    }
+  }
+  __syncthreads();
+
+  // One CTA per kv head stores the new cache row; every CTA attends the current
+  // token from the FP32 values above, never from the row being written.
+  if (fuse_kv && blockIdx.z == 0 && split == static_cast<int>(pos % n_split)) {
+    const size_t off = (static_cast<size_t>(pos) * n_kv + kvh) * hd;
+    __nv_bfloat16 *kc = const_cast<__nv_bfloat16 *>(k_cache) + off;
+    __nv_bfloat16 *vc = const_cast<__nv_bfloat16 *>(v_cache) + off;
+    const __nv_bfloat16 *va = v_act + static_cast<size_t>(kvh) * hd;
+    for (int d = tid; d < hd; d += kAttnThreads) {
+      kc[d] = __float2bfloat16(krot[d]);
+      vc[d] = va[d];
+    }
+  }
+
+  // Lane owns elements d = 2*lane + 64*p (+0, +1).
+  float qreg[H][2 * P];
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      const int d = 2 * lane + 64 * p;
+      const bool live = h < nh && d < hd;
+      qreg[h][2 * p] = live ? qrot[h][d] : 0.f;
+      qreg[h][2 * p + 1] = live ? qrot[h][d + 1] : 0.f;
+    }
+  }
+
+  float m[H], l[H], acc[H][2 * P];
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+    m[h] = kNegInit;
+    l[h] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 2 * P; ++e) acc[h][e] = 0.f;
+  }
+
+  for (int t = split + warp * n_split; t < vl; t += kAttnWarps * n_split) {
+    const bool cur = fuse_kv && t == pos;
+    const size_t row = (static_cast<size_t>(t) * n_kv + kvh) * hd;
+    float kk[2 * P], vv[2 * P];
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      const int d = 2 * lane + 64 * p;
+      if (d < hd) {
+        if (cur) {
+          kk[2 * p] = krot[d];
+          kk[2 * p + 1] = krot[d + 1];
+          vv[2 * p] = vcur[d];
+          vv[2 * p + 1] = vcur[d + 1];
+        } else {
+          const uint32_t kb = __ldg(reinterpret_cast<const uint32_t *>(k_cache + row + d));
+          const uint32_t vb = __ldg(reinterpret_cast<const uint32_t *>(v_cache + row + d));
+          kk[2 * p] = bf16_lo(kb);
+          kk[2 * p + 1] = bf16_hi(kb);
+          vv[2 * p] = bf16_lo(vb);
+          vv[2 * p + 1] = bf16_hi(vb);
+        }
+      } else {
+        kk[2 * p] = kk[2 * p + 1] = vv[2 * p] = vv[2 * p + 1] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+      float dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < 2 * P; ++e) dot = fmaf(qreg[h][e], kk[e], dot);
+      dot = warp_sum_xor(dot) * scale;
+      const float m2 = fmaxf(m[h], dot);
+      const float alpha = __expf(m[h] - m2);
+      const float ex = __expf(dot - m2);
+      l[h] = l[h] * alpha + ex;
+#pragma unroll
+      for (int e = 0; e < 2 * P; ++e) acc[h][e] = acc[h][e] * alpha + ex * vv[e];
+      m[h] = m2;
+    }
+  }
+
+  // Combine the four warps, in warp order, into this split's (m, l, o).
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+    if (lane == 0) {
+      sm_m[warp][h] = m[h];
+      sm_l[warp][h] = l[h];
+    }
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      const int d = 2 * lane + 64 * p;
+      sm_o[warp][h][d] = acc[h][2 * p];
+      sm_o[warp][h][d + 1] = acc[h][2 * p + 1];
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < nh * hd; i += kAttnThreads) {
+    const int h = i / hd;
+    const int d = i - h * hd;
+    float mm = kNegInit;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm_m[w][h]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float a = __expf(sm_m[w][h] - mm);
+      ll += a * sm_l[w][h];
+      oo += a * sm_o[w][h][d];
+    }
+    const size_t slot = static_cast<size_t>(h_first + h) * n_split + split;
+    o_s[slot * hd + d] = oo;
+    if (d == 0) {
+      m_s[slot] = mm;
+      l_s[slot] = ll;
+    }
+  }
+}
+
+__global__ void attn_merge_kernel(const float *__restrict__ m_s, const float *__restrict__ l_s,
+                                  const float *__restrict__ o_s, __nv_bfloat16 *__restrict__ out,
+                                  int hd, int n_split) {
+  const int head = blockIdx.x;
+  const float *mh = m_s + static_cast<size_t>(head) * n_split;
+  const float *lh = l_s + static_cast<size_t>(head) * n_split;
+  float m = kNegInit;
+  for (int s = 0; s < n_split; ++s) m = fmaxf(m, mh[s]);
+  float l = 0.f;
+  for (int s = 0; s < n_split; ++s) l += __expf(mh[s] - m) * lh[s];
+  __nv_bfloat16 *dst = out + static_cast<size_t>(head) * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+      o += __expf(mh[s] - m) * o_s[(static_cast<size_t>(head) * n_split + s) * hd + d];
+    }
+    dst[d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Packed embedding rows  (reference: gpu/host/embedding.py:74-107)
+// ----------------------------------------------------------------------------
+__global__ void embed_rows_kernel(const uint8_t *__restrict__ packed,
+                                  const uint16_t *__restrict__ scale,
+                                  const int64_t *__restrict__ ids, __nv_bfloat16 *__restrict__ out,
+                                  int32_t *status, const int64_t *position, int32_t *valid_len,
+                                  int M, int K, int K_pad) {
+  const int r = blockIdx.y;
+  if (r == 0 && blockIdx.x == 0 && threadIdx.x == 0 && position != nullptr &&
+      valid_len != nullptr) {
+    *valid_len = static_cast<int32_t>(*position + 1);
+  }
+  const long long id = ids[r];
+  const bool bad = id < 0 || id >= M;
+  if (bad && blockIdx.x == 0 && threadIdx.x == 0 && status != nullptr) *status = 1;
+  // one thread per 8 codes (4 packed bytes -> 16 bytes of bf16)
+  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = c8 * 8;
+  if (k >= K) return;
+  __nv_bfloat16 vals[8];
+  if (bad) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) vals[e] = __float2bfloat16(0.f);
+  } else {
+    const uint32_t pk = *reinterpret_cast<const uint32_t *>(
+        packed + static_cast<size_t>(id) * (K_pad >> 1) + (k >> 1));
+    const float s =
+        half_bits_to_float(scale[static_cast<size_t>(id) * (K_pad / kGroup) + (k >> 6)]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const uint32_t code = (pk >> (4 * e)) & 0xFu;
+      vals[e] = __float2bfloat16(__uint_as_float(kLutBits[code]) * s);
+    }
+  }
+  __nv_bfloat16 *dst = out + static_cast<size_t>(r) * K + k;
+  if (k + 8 <= K && (K & 7) == 0) {
+    *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(vals);
+  } else {
+    for (int e = 0; e < 8 && k + e < K; ++e) dst[e] = vals[e];
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Greedy pick + commit  (reference: gpu/decodev2/step.py:182, state.py:98-103)
+// ----------------------------------------------------------------------------
+constexpr int kPickThreads = 256;
+
+__device__ __forceinline__ unsigned long long pick_key(uint32_t bf16_bits, int idx) {
+  uint32_t b = bf16_bits & 0xFFFFu;
+  uint32_t ord;
+  if ((b & 0x7FFFu) > 0x7F80u) {
+    ord = 0xFFFFu;  // NaN ranks above everything, as torch.argmax does
+  } else {
+    if (b == 0x8000u) b = 0u;  // -0 equals +0
+    ord = (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);
+  }
+  return (static_cast<unsigned long long>(ord) << 32) |
+         static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(idx));
+}
+
+__global__ void __launch_bounds__(kPickThreads)
+pick_commit_kernel(const __nv_bfloat16 *__restrict__ logits, int n, int64_t *next_token,
+                   int64_t *token, int64_t *position, uint8_t *finished, int64_t eos,
+                   unsigned long long *best, unsigned int *ticket) {
+  __shared__ unsigned long long red[kPickThreads / 32];
+  __shared__ bool last;
+  unsigned long long key = 0ull;
+  const int stride = gridDim.x * kPickThreads;
+  for (int i = blockIdx.x * kPickThreads + threadIdx.x; i < n; i += stride) {
+    const unsigned long long cand = pick_key(__bfloat16_as_ushort(logits[i]), i);
+    key = cand > key ? cand : key;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, key, off);
+    key = o > key ? o : key;
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = key;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 1; i < kPickThreads / 32; ++i) key = red[i] > key ? red[i] : key;
+    atomicMax(best, key);
+    __threadfence();
+    last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    if (last) {
+      __threadfence();
+      const unsigned long long win = atomicMax(best, 0ull);
+      const int64_t idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(win));
+      *next_token = idx;
+      if (token != nullptr) *token = idx;
+      if (position != nullptr) *position += 1;
+      if (finished != nullptr && idx == eos) *finished |= 1;
+      *best = 0ull;
+      *ticket = 0u;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace chr
+
+using namespace chr;
+
+extern "C" int chr_nf4_rms(const void *x, const void *w, void *y, int32_t n, float eps,
+                           void *stream) {
+  if (x == nullptr || w == nullptr || y == nullptr) return kNull;
+  if (n < 1) return kDims;
+  rms_kernel<<<1, kRmsThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(w),
+      static_cast<__nv_bfloat16 *>(y), n, eps);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+}
+
+extern "C" int chr_nf4_rope_kv(void *q, void *k, const void *v, void *k_cache, void *v_cache,
+                               const void *cos, const void *sin, const void *position,
+                               int32_t n_q, int32_t n_kv, int32_t hd, int32_t max_seq,
+                               void *stream) {
+  if (q == nullptr || k == nullptr || v == nullptr || k_cache == nullptr || v_cache == nullptr ||
+      cos == nullptr || sin == nullptr || position == nullptr) {
+    return kNull;
+  }
+  if (n_q < 1 || n_kv < 1 || hd < 2 || (hd & 1) != 0 || max_seq < 1) return kDims;
+  rope_kv_kernel<<<static_cast<unsigned>(n_q + n_kv), 64, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16 *>(q), static_cast<__nv_bfloat16 *>(k),
+      static_cast<const __nv_bfloat16 *>(v), static_cast<__nv_bfloat16 *>(k_cache),
+      static_cast<__nv_bfloat16 *>(v_cache), static_cast<const __nv_bfloat16 *>(cos),
+      static_cast<const __nv_bfloat16 *>(sin), static_cast<const int64_t *>(position), n_q, n_kv,
+      hd, max_seq);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+}
+
+extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *out,
+                            const void *valid_len, float *ws, int32_t n_q, int32_t n_kv,
+                            int32_t hd, int32_t n_split, float scale, void *stream,
+                            const void *k_act, const void *v_act, const void *cos,
+                            const void *sin, const void *position, int32_t max_seq) {
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || valid_len == nullptr ||
+      ws == nullptr) {
+    return kNull;
+  }
+  if (n_q < 1 || n_kv < 1 || hd < 2 || hd > 256 || (hd & 1) != 0 || (n_q % n_kv) != 0 ||
+      n_split < 1 || n_split > 64 || max_seq < 1) {
+    return kDims;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int slots = n_q * n_split;
+  float *m_s = ws;
+  float *l_s = ws + slots;
+  float *o_s = ws + 2 * slots;
+  const int n_rep = n_q / n_kv;
+  auto *qp = static_cast<const __nv_bfloat16 *>(q);
+  auto *kp = static_cast<const __nv_bfloat16 *>(k);
+  auto *vp = static_cast<const __nv_bfloat16 *>(v);
+  auto *vl = static_cast<const int32_t *>(valid_len);
+  auto *ka = static_cast<const __nv_bfloat16 *>(k_act);
+  auto *va = static_cast<const __nv_bfloat16 *>(v_act);
+  auto *cp = static_cast<const __nv_bfloat16 *>(cos);
+  auto *sp = static_cast<const __nv_bfloat16 *>(sin);
+  auto *pp = static_cast<const int64_t *>(position);
+
+#define CHR_ATTN(PP, HH)                                                                       \
+  attn_split_kernel<PP, HH>                                                                    \
+      <<<dim3(static_cast<unsigned>(n_split), static_cast<unsigned>(n_kv),                     \
+              static_cast<unsigned>((n_rep + HH - 1) / HH)),                                   \
+         kAttnThreads, 0, st>>>(qp, kp, vp, m_s, l_s, o_s, vl, ka, va, cp, sp, pp, n_q, n_kv,  \
+                                hd, n_split, max_seq, scale)
+  if (hd <= 64) {
+    CHR_ATTN(1, 8);
+  } else if (hd <= 128) {
+    CHR_ATTN(2, 8);
+  } else {
+    CHR_ATTN(4, 4);
+  }
+#undef CHR_ATTN
+  attn_merge_kernel<<<static_cast<unsigned>(n_q), 128, 0, st>>>(
+      m_s, l_s, o_s, static_cast<__nv_bfloat16 *>(out), hd, n_split);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+}
+
+extern "C" int chr_nf4_embed_rows(const chr_nf4_dev_t *w, const void *ids, int32_t n, void *out,
+                                  void *status, const void *position, void *valid_len,
+                                  void *stream) {
+  if (w == nullptr || ids == nullptr || out == nullptr) return kNull;
+  const int rc = check_matrix(w);
+  if (rc != kOk) return rc;
+  if (n < 1 || n > 65535) return kRangeN;
+  if (!aligned(w->packed, 16) || !aligned(out, 16)) return kAlign;
+  const int c8 = (w->K + 7) / 8;
+  const int threads = 128;
+  const dim3 grid(static_cast<unsigned>((c8 + threads - 1) / threads), static_cast<unsigned>(n));
+  embed_rows_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      w->packed, w->scale, static_cast<const int64_t *>(ids), static_cast<__nv_bfloat16 *>(out),
+      static_cast<int32_t *>(status), static_cast<const int64_t *>(position),
+      static_cast<int32_t *>(valid_len), w->M, w->K, w->K_pad);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+}
+
+extern "C" int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_token, void *token,
+                                   void *position, void *finished, int64_t eos, void *scratch,
+                                   void *stream) {
+  if (logits == nullptr || next_token == nullptr || scratch == nullptr) return kNull;
+  if (n < 1) return kDims;
+  if (!aligned(scratch, 8)) return kAlign;
+  int blocks = (n + kPickThreads * 8 - 1) / (kPickThreads * 8);
+  const int sms = sm_count();
+  blocks = blocks < 1 ? 1 : (blocks > sms ? sms : blocks);
+  auto *best = static_cast<unsigned long long *>(scratch);
+  auto *ticket = reinterpret_cast<unsigned int *>(best + 1);
+  pick_commit_kernel<<<static_cast<unsigned>(blocks), kPickThreads, 0,
+                       static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16 *>(logits), n, static_cast<int64_t *>(next_token),
+      static_cast<int64_t *>(token), static_cast<int64_t *>(position),
+      static_cast<uint8_t *>(finished), eos, best, ticket);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+}

@@ -1,0 +1,113 @@
+// Shared device/host helpers for the sm_100a NF4 kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "chr_gpu.h"
+
+namespace chr {
+
+constexpr int kGroup = 64;
+
+// Return codes of the C ABI (reference: gpu/include/chr_gpu.h:30-33).
+enum Rc : int {
+  kOk = 0,
+  kNull = -1,
+  kRangeN = -2,
+  kDims = -3,
+  kKPad = -4,
+  kAlign = -5,
+  kLaunch = -6,
+  kWorkspace = -7,
+  kNonFinite = -8,
+};
+
+// binary32 bit patterns of the sixteen NF4 levels (docs/spec/nf4.md:37-54).
+__device__ __constant__ uint32_t kLutBits[16] = {
+    0xBF800000u, 0xBF3239B1u, 0xBF066B30u, 0xBECA32A0u, 0xBE91A24Du, 0xBE3D353Fu,
+    0xBDBA7871u, 0x00000000u, 0x3DA2FAFFu, 0x3E24CAE3u, 0x3E7C04DDu, 0x3EAD033Au,
+    0x3EE1A4B8u, 0x3F1007ABu, 0x3F3913B3u, 0x3F800000u,
+};
+
+inline bool k_pad_ok(int K, int K_pad) {
+  return K >= 1 && K_pad >= K && K_pad == kGroup * ((K + kGroup - 1) / kGroup);
+}
+
+inline bool aligned(const void *p, uintptr_t a) {
+  return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
+}
+
+inline int check_matrix(const chr_nf4_dev_t *w) {
+  if (w == nullptr) return kNull;
+  if (w->M < 1 || w->K < 1 || w->packed == nullptr || w->scale == nullptr) return kDims;
+  if (!k_pad_ok(w->K, w->K_pad)) return kKPad;
+  return kOk;
+}
+
+inline int sm_count() {
+  static int cached = 0;
+  if (cached > 0) return cached;
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) {
+    return 148;
+  }
+  cached = n;
+  return n;
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+
+__device__ __forceinline__ float half_bits_to_float(uint16_t h) {
+  return __half2float(__ushort_as_half(h));
+}
+
+// 16-byte streaming load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint16_t ld_stream_u16(const void *p) {
+  uint16_t v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+
+// Two FP32 fused multiply-adds in one instruction (sm_100 packed FP32).
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  unsigned long long ra = *reinterpret_cast<unsigned long long *>(&a);
+  unsigned long long rb = *reinterpret_cast<unsigned long long *>(&b);
+  unsigned long long rc = *reinterpret_cast<unsigned long long *>(&c);
+  unsigned long long rd;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  return *reinterpret_cast<float2 *>(&rd);
+}
+
+__device__ __forceinline__ float2 lds_f2(uint32_t saddr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(saddr));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum_xor(float v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max_xor(float v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+}  // namespace chr

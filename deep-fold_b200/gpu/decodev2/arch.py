@@ -1,0 +1,130 @@
+"""Decoder architectures the executors can drive.
+
+``ArchSpec`` keeps the field names and derived properties of the reference's
+spec (gpu/decodev2/plan.py:17-78) so states, weights and tests read the same.
+Besides the reference's three toy specs this module carries the four
+checkpoint-shaped configurations the benchmarks use (random-init weights).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+
+__all__ = [
+    "ArchSpec",
+    "TINY_LLAMA",
+    "TINY_INTERNLM",
+    "MEDIUM_LLAMA",
+    "QWEN25_3B",
+    "QWEN25_14B",
+    "INTERNLM25_20B",
+    "QWEN25_32B",
+    "CONFIGS",
+    "with_max_seq",
+]
+
+_FAMILIES = ("llama_swiglu", "internlm_gqa")
+
+
+@dataclass(frozen=True)
+class ArchSpec:
+    """``llama_swiglu``: split q/k/v (+bias allowed); ``internlm_gqa``: fused wqkv
+    whose rows are grouped per kv head as [n_rep q heads, k, v]."""
+
+    name: str
+    family: str
+    n_layers: int
+    hidden: int
+    n_q: int
+    n_kv: int
+    head_dim: int
+    intermediate: int
+    vocab: int
+    max_seq: int
+    rms_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    eos_id: int = 2
+    tied_embed: bool = False
+    qkv_bias: bool = False
+
+    def __post_init__(self) -> None:
+        if self.family not in _FAMILIES:
+            raise ValueError(f"unsupported family {self.family!r}")
+        if self.n_layers < 1 or self.max_seq < 2:
+            raise ValueError("need at least one layer and max_seq>=2")
+        if self.hidden != self.n_q * self.head_dim:
+            raise ValueError(f"hidden {self.hidden} != n_q*head_dim {self.n_q * self.head_dim}")
+        if self.n_q % self.n_kv:
+            raise ValueError(f"n_q={self.n_q} is not a multiple of n_kv={self.n_kv}")
+        if self.head_dim % 2:
+            raise ValueError("RoPE needs even head_dim")
+        if self.hidden % 64 or self.intermediate % 64:
+            raise ValueError("hidden and intermediate must be multiples of NF4 group 64")
+        if not 0 <= self.eos_id < self.vocab:
+            raise ValueError(f"eos_id {self.eos_id} out of vocab {self.vocab}")
+
+    @property
+    def n_rep(self) -> int:
+        return self.n_q // self.n_kv
+
+    @property
+    def q_dim(self) -> int:
+        return self.n_q * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.n_kv * self.head_dim
+
+    @property
+    def wqkv_out(self) -> int:
+        return (self.n_q + 2 * self.n_kv) * self.head_dim
+
+    @property
+    def attn_scale(self) -> float:
+        return self.head_dim**-0.5
+
+    def linear_shapes(self) -> dict[str, tuple[int, int]]:
+        """(M, K) of every linear of one layer plus lm_head."""
+        h, i = self.hidden, self.intermediate
+        out: dict[str, tuple[int, int]] = {}
+        if self.family == "internlm_gqa":
+            out["wqkv"] = (self.wqkv_out, h)
+        else:
+            out.update(q=(self.q_dim, h), k=(self.kv_dim, h), v=(self.kv_dim, h))
+        out.update(o=(h, self.q_dim), gate=(i, h), up=(i, h), down=(h, i), lm_head=(self.vocab, h))
+        return out
+
+    def packed_bytes_per_token(self) -> int:
+        """NF4 bytes (codes + scales) one decode step reads: all layers + lm_head."""
+        per = lambda m, k: m * k // 2 + m * (k // 64) * 2
+        shapes = self.linear_shapes()
+        layer = sum(per(*mk) for name, mk in shapes.items() if name != "lm_head")
+        return self.n_layers * layer + per(*shapes["lm_head"])
+
+
+def with_max_seq(spec: ArchSpec, max_seq: int) -> ArchSpec:
+    return replace(spec, max_seq=int(max_seq))
+
+
+TINY_LLAMA = ArchSpec("tiny-llama", "llama_swiglu", 2, 64, 4, 2, 16, 128, 32, 16)
+TINY_INTERNLM = ArchSpec("tiny-internlm", "internlm_gqa", 2, 64, 4, 2, 16, 128, 32, 16)
+MEDIUM_LLAMA = ArchSpec("medium-llama", "llama_swiglu", 4, 512, 8, 2, 64, 1024, 128, 32)
+
+QWEN25_3B = ArchSpec(
+    "qwen2.5-3b-arch", "llama_swiglu", 36, 2048, 16, 2, 128, 11008, 151936, 2048,
+    rope_theta=1.0e6, eos_id=151645, tied_embed=True, qkv_bias=True,
+)
+QWEN25_14B = ArchSpec(
+    "qwen2.5-14b-arch", "llama_swiglu", 48, 5120, 40, 8, 128, 13824, 152064, 2048,
+    rope_theta=1.0e6, eos_id=151645, qkv_bias=True,
+)
+INTERNLM25_20B = ArchSpec(
+    "internlm2.5-20b-arch", "internlm_gqa", 48, 6144, 48, 8, 128, 16384, 92544, 2048,
+    rms_eps=1e-5, rope_theta=1.0e6, eos_id=2,
+)
+QWEN25_32B = ArchSpec(
+    "qwen2.5-32b-arch", "llama_swiglu", 64, 5120, 40, 8, 128, 27648, 152064, 2048,
+    rope_theta=1.0e6, eos_id=151645, qkv_bias=True,
+)
+
+CONFIGS = {s.name: s for s in (QWEN25_3B, QWEN25_14B, INTERNLM25_20B, QWEN25_32B)}

@@ -1,0 +1,86 @@
+"""Chunked prompt prefill: tensor-core NF4 GEMM for the linears, eager (not captured).
+
+Follows the reference (gpu/decodev2/prefill.py:26-141): chunks of at most
+``LIVE_MAX_N`` positions, RMSNorm / RoPE / causal GQA attention as torch ops in
+the cache dtype, KV rows written by slice, lm_head only on the last chunk.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from gpu.nf4 import LIVE_MAX_N
+
+from .arch import ArchSpec
+from .embed import gather_embed
+from .linear import DeviceLayer, DeviceWeights, nf4_linear
+from .rope import apply_rope_torch
+from .state import DecodeState
+
+__all__ = ["forward_prefill", "prefill_chunk_width"]
+
+
+def prefill_chunk_width(state: DecodeState, chunk: int | None = None) -> int:
+    cap = min(int(LIVE_MAX_N), int(state.spec.max_seq))
+    return cap if chunk is None else max(1, min(int(chunk), cap))
+
+
+def _split_qkv(layer: DeviceLayer, h: torch.Tensor, spec: ArchSpec):
+    n = int(h.shape[0])
+    if spec.family == "internlm_gqa":
+        y = nf4_linear(layer.wqkv, h).view(n, spec.n_kv, spec.n_rep + 2, spec.head_dim)
+        q = y[:, :, : spec.n_rep].reshape(n, spec.n_q, spec.head_dim)
+        return q, y[:, :, -2], y[:, :, -1]
+    return (
+        nf4_linear(layer.q, h).view(n, spec.n_q, spec.head_dim),
+        nf4_linear(layer.k, h).view(n, spec.n_kv, spec.head_dim),
+        nf4_linear(layer.v, h).view(n, spec.n_kv, spec.head_dim),
+    )
+
+
+def _attend(q, k, v, spec: ArchSpec, mask) -> torch.Tensor:
+    """``q`` [n, n_q, hd]; ``k``/``v`` [1, n_kv, seq, hd]; bool mask [1, 1, n, seq]."""
+    n = int(q.shape[0])
+    a = F.scaled_dot_product_attention(
+        q.permute(1, 0, 2).unsqueeze(0), k, v, attn_mask=mask, scale=spec.attn_scale,
+        enable_gqa=spec.n_q != spec.n_kv,
+    )
+    return a.squeeze(0).permute(1, 0, 2).reshape(n, spec.q_dim)
+
+
+def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch.Tensor,
+                    start: int, *, logits: bool = True) -> None:
+    """Teacher-force ``token_ids`` into KV slots ``start..start+n-1``."""
+    spec = state.spec
+    ids = token_ids.reshape(-1).to(device=state.device, dtype=torch.long)
+    n = int(ids.numel())
+    if n < 1:
+        raise ValueError("prefill chunk must be non-empty")
+    start = int(start)
+    seq = start + n
+    if seq > spec.max_seq:
+        raise ValueError(f"prefill {start}..{seq} exceeds max_seq={spec.max_seq}")
+    dtype = state.arena.x.dtype
+    x = gather_embed(weights.embed, ids, dtype=dtype)
+    cos, sin = state.cos[start:seq], state.sin[start:seq]
+    q_pos = torch.arange(start, seq, device=state.device).unsqueeze(1)
+    mask = (torch.arange(seq, device=state.device).unsqueeze(0) <= q_pos)[None, None]
+    for li, layer in enumerate(weights.layers):
+        h = F.rms_norm(x, layer.norm1.shape, layer.norm1, spec.rms_eps)
+        q, k, v = _split_qkv(layer, h, spec)
+        q = apply_rope_torch(q, cos, sin)
+        k = apply_rope_torch(k, cos, sin)
+        state.kv.write_range(li, start, k, v)
+        k_all, v_all = state.kv.view(li, seq)
+        x = x + nf4_linear(layer.o, _attend(q, k_all, v_all, spec, mask))
+        h = F.rms_norm(x, layer.norm2.shape, layer.norm2, spec.rms_eps)
+        x = x + nf4_linear(layer.down, F.silu(nf4_linear(layer.gate, h)) * nf4_linear(layer.up, h))
+    state.position.fill_(seq)
+    state.valid_len.fill_(seq)
+    if not logits:
+        return
+    hidden = F.rms_norm(x[-1:], weights.final_norm.shape, weights.final_norm, spec.rms_eps)
+    out = nf4_linear(weights.lm_head, hidden)
+    state.arena.logits[0].copy_(out.reshape(-1))
+    state.next_token.copy_(out.argmax(dim=-1).reshape(()).to(dtype=torch.int64))

@@ -1,0 +1,139 @@
+"""ctypes binding of ``libchr_nf4.so`` (the C ABI declared in ``include/chr_gpu.h``).
+
+There is no fallback: if the library is missing or an entry point is absent the
+import of any op fails loudly. Build it with ``python deep-fold_b200/csrc/build.py``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+_DIR = Path(__file__).resolve().parent
+LIB_PATH = _DIR / "libchr_nf4.so"
+
+
+class ChrNf4Dev(Structure):
+    """Mirror of ``chr_nf4_dev_t``; field order is frozen."""
+
+    _fields_ = [
+        ("M", c_int32),
+        ("K", c_int32),
+        ("K_pad", c_int32),
+        ("packed", c_void_p),
+        ("scale", c_void_p),
+    ]
+
+
+class ChrNf4Plan(Structure):
+    """Mirror of ``chr_nf4_plan_t``."""
+
+    _fields_ = [
+        ("path", c_int32),
+        ("grid_x", c_int32),
+        ("grid_y", c_int32),
+        ("block", c_int32),
+        ("bm", c_int32),
+        ("bk", c_int32),
+        ("n_ktiles", c_int32),
+        ("tiles_per_split", c_int32),
+        ("ctas", c_int32),
+        ("smem_bytes", c_int32),
+        ("ws_floats", c_int64),
+    ]
+
+
+_DEV = POINTER(ChrNf4Dev)
+
+# name -> (restype, argtypes); every symbol include/chr_gpu.h declares.
+SIGNATURES = {
+    "chr_nf4_gemm": (c_int, [_DEV, c_void_p, c_void_p, c_int32, c_void_p]),
+    "chr_nf4_gemm_plan": (c_int, [_DEV, c_int32, c_int32, POINTER(ChrNf4Plan)]),
+    "chr_nf4_gemm_ws": (c_int, [_DEV, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p]),
+    "chr_nf4_gemm_ws_max": (
+        c_int,
+        [_DEV, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int32],
+    ),
+    "chr_nf4_set_tuning": (None, [c_int32, c_int32, c_int32]),
+    "chr_nf4_gemv": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
+    "chr_nf4_gemv_qkv": (
+        c_int,
+        [_DEV, _DEV, _DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_float],
+    ),
+    "chr_nf4_gemv_swiglu": (
+        c_int, [_DEV, _DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_float]
+    ),
+    "chr_nf4_rope_kv": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int32, c_int32, c_int32, c_int32, c_void_p],
+    ),
+    "chr_nf4_attn": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+         c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_int32],
+    ),
+    "chr_nf4_rms": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_float, c_void_p]),
+    "chr_nf4_version": (c_char_p, []),
+    "chr_nf4_embed_rows": (
+        c_int, [_DEV, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    ),
+    "chr_nf4_pick_commit": (
+        c_int,
+        [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
+    ),
+    "chr_nf4_encode_f32": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int32]),
+    "chr_nf4_decode_f32": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_int32]),
+    "chr_nf4_encode_dev": (
+        c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]
+    ),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once and type every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.is_file():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: the NF4 ops have no fallback. "
+            "Build it with `python deep-fold_b200/csrc/build.py`."
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise RuntimeError(f"{LIB_PATH.name} does not export {name}") from exc
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+_RC_TEXT = {
+    0: "ok",
+    -1: "null pointer",
+    -2: "N out of range (live 1..32, plan 1..64)",
+    -3: "invalid M/K or null packed/scale",
+    -4: "K_pad != 64*ceil(K/64)",
+    -5: "packed or x not 16-byte aligned",
+    -6: "CUDA launch / func attribute failed",
+    -7: "split-K workspace smaller than the plan asked for",
+    -8: "non-finite value in encoder input",
+}
+
+
+def rc_text(rc: int) -> str:
+    return _RC_TEXT.get(int(rc), "unknown error")
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed ({rc}): {rc_text(rc)}")

@@ -1,0 +1,176 @@
+/* C ABI of the B200 (sm_100a) NF4 fused-dequant linear path.
+ *
+ * The first block of declarations is the interface deep-fold's Python side
+ * binds for this path (reference: gpu/include/chr_gpu.h); struct layouts, entry
+ * names, argument order and return codes are kept so that the reference's
+ * binding layer can call this library unchanged. The second block is additive:
+ * entries the reference does not have (batched GEMV, embedding row decode,
+ * fused greedy pick). Nothing here takes or returns a framework type: plain
+ * pointers, sizes and a cudaStream_t passed as void*.
+ *
+ * Ownership: the caller owns every buffer, including split-K and attention
+ * workspaces. No entry point allocates device memory. Return codes, shared by
+ * every int-returning entry (reference: gpu/include/chr_gpu.h:30-33):
+ *    0 ok            -1 null pointer          -2 N out of range
+ *   -3 bad dims or null packed/scale          -4 K_pad != 64*ceil(K/64)
+ *   -5 alignment (packed and x 16 B, scale 2 B)
+ *   -6 CUDA launch or attribute failure       -7 workspace too small
+ */
+#pragma once
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* Interface kept from the reference                                         */
+/* ------------------------------------------------------------------------ */
+
+/* One NF4 group-64 matrix resident on the device. Field order is frozen
+ * (reference: gpu/include/chr_gpu.h:11-17). Byte packed[r][c] holds W[r][2c] in
+ * its low nibble and W[r][2c+1] in its high nibble; scale[r][g] covers columns
+ * 64g..64g+63 of row r. Columns K..K_pad-1 exist in the blobs and are ignored. */
+typedef struct {
+  int32_t M;              /* logical out_features */
+  int32_t K;              /* logical in_features */
+  int32_t K_pad;          /* 64 * ceil(K / 64) */
+  const uint8_t *packed;  /* device, [M, K_pad/2] row-major */
+  const uint16_t *scale;  /* device, [M, K_pad/64], IEEE binary16 bits */
+} chr_nf4_dev_t;
+
+/* Launch description returned by chr_nf4_gemm_plan (reference:
+ * gpu/include/chr_gpu.h:48-61; same fields, sm_100a tile values). */
+typedef struct {
+  int32_t path;            /* 0 tcgen05 tile, BN from N; see CHR_PATH_* below */
+  int32_t grid_x;          /* ceil(M / bm) */
+  int32_t grid_y;          /* split_k */
+  int32_t block;           /* threads per CTA */
+  int32_t bm;              /* rows of M per CTA */
+  int32_t bk;              /* K per pipeline stage */
+  int32_t n_ktiles;        /* ceil(K_pad / bk) */
+  int32_t tiles_per_split; /* K tiles one CTA walks */
+  int32_t ctas;            /* grid_x * grid_y */
+  int32_t smem_bytes;      /* dynamic shared memory per CTA */
+  int64_t ws_floats;       /* FP32 partials the caller must supply; 0 if grid_y == 1 */
+} chr_nf4_plan_t;
+
+/* y[M,N] = bf16( sum_k bf16(LUT[code]*scale)[m,k] * x[k,n] ), FP32 accumulate.
+ * x: bf16 [K, N] row-major (N fastest); y: bf16 [M, N]. N in [1, 32] for the
+ * two plain entries, up to max_n (<= 64) for chr_nf4_gemm_ws_max.
+ * Replaces gpu/include/chr_gpu.h:34 (chr_nf4_gemm), :72 (chr_nf4_gemm_ws),
+ * :77 (chr_nf4_gemm_ws_max), :66 (chr_nf4_gemm_plan), :86 (chr_nf4_set_tuning);
+ * kernels gpu/nf4/nf4_gemm.cu:1108-1130,1428-1450. */
+int chr_nf4_gemm(const chr_nf4_dev_t *w, const void *x, void *y, int32_t N,
+                 void *stream);
+int chr_nf4_gemm_plan(const chr_nf4_dev_t *w, int32_t N, int32_t have_ws,
+                      chr_nf4_plan_t *out);
+int chr_nf4_gemm_ws(const chr_nf4_dev_t *w, const void *x, void *y, int32_t N,
+                    float *ws, int64_t ws_floats, void *stream);
+int chr_nf4_gemm_ws_max(const chr_nf4_dev_t *w, const void *x, void *y, int32_t N,
+                        float *ws, int64_t ws_floats, void *stream, int32_t max_n);
+/* path: 0 auto; split_k: 0 auto, >0 forced (clamped to the K tiles);
+ * one_wave: SM count the split-K target is expressed in, 0 = this device. */
+void chr_nf4_set_tuning(int32_t path, int32_t split_k, int32_t one_wave);
+
+/* y[M] = bf16( sum_k (LUT[code]*scale)[m,k] * x[k] (+ add[m]) ), everything
+ * FP32 until the single final rounding; weights are NOT rounded to bf16.
+ * x bf16 [K]; y bf16 [M]; add optional bf16 [M], may alias y; rms_w optional
+ * bf16 [K]: RMSNorm(x, rms_w, rms_eps) is applied to x first (rounded to bf16,
+ * as a separate rms kernel would).
+ * Replaces gpu/include/chr_gpu.h:94 ; kernel gpu/nf4/nf4_gemv.cu:291-324. */
+int chr_nf4_gemv(const chr_nf4_dev_t *w, const void *x, void *y, void *stream,
+                 const void *add, const void *rms_w, float rms_eps);
+
+/* Three GEMVs sharing x in one launch, each with an optional bf16 bias [M].
+ * q, k, v must share K and K_pad.
+ * Replaces gpu/include/chr_gpu.h:101 ; kernel gpu/nf4/nf4_gemv.cu:326-390. */
+int chr_nf4_gemv_qkv(const chr_nf4_dev_t *q, const chr_nf4_dev_t *k,
+                     const chr_nf4_dev_t *v, const void *x, void *yq, void *yk,
+                     void *yv, const void *bq, const void *bk, const void *bv,
+                     void *stream, const void *rms_w, float rms_eps);
+
+/* y[M] = bf16( silu(gate.x) * (up.x) ), silu(t) = t / (1 + expf(-t)).
+ * Replaces gpu/include/chr_gpu.h:109 ; kernel gpu/nf4/nf4_gemv.cu:392-495. */
+int chr_nf4_gemv_swiglu(const chr_nf4_dev_t *gate, const chr_nf4_dev_t *up,
+                        const void *x, void *y, void *stream, const void *rms_w,
+                        float rms_eps);
+
+/* In-place rotate-half RoPE on q [n_q,hd] and k [n_kv,hd] (rounded to bf16),
+ * then k and v are written to cache row *position. cos/sin bf16 [max_seq,hd];
+ * position: device int64. A position outside [0,max_seq) writes nothing.
+ * Replaces gpu/include/chr_gpu.h:116 ; kernel gpu/nf4/nf4_gemv.cu:497-537. */
+int chr_nf4_rope_kv(void *q, void *k, const void *v, void *k_cache, void *v_cache,
+                    const void *cos, const void *sin, const void *position,
+                    int32_t n_q, int32_t n_kv, int32_t hd, int32_t max_seq,
+                    void *stream);
+
+/* GQA decode attention over cache rows t < *valid_len (device int32).
+ * k, v: bf16 cache [max_seq, n_kv, hd]; q bf16 [n_q, hd]; out bf16 [n_q*hd];
+ * ws: FP32 workspace of at least n_q*n_split*(hd+2) floats. With cos, sin and
+ * position (device int64) q is rotated in FP32; with k_act/v_act as well, the
+ * rotated current k and the current v are written to cache row *position and
+ * the current token is attended with those unrounded FP32 values.
+ * hd <= 256, hd % 8 == 0, n_split in [1, 64].
+ * Replaces gpu/include/chr_gpu.h:123 ; kernels gpu/nf4/nf4_gemv.cu:599-727. */
+int chr_nf4_attn(const void *q, const void *k, const void *v, void *out,
+                 const void *valid_len, float *ws, int32_t n_q, int32_t n_kv,
+                 int32_t hd, int32_t n_split, float scale, void *stream,
+                 const void *k_act, const void *v_act, const void *cos,
+                 const void *sin, const void *position, int32_t max_seq);
+
+/* y[i] = bf16( w[i] * x[i] * rsqrt(mean(x^2) + eps) ); x, w, y bf16 [n].
+ * Replaces gpu/include/chr_gpu.h:133 ; kernel gpu/nf4/nf4_gemv.cu:729-751. */
+int chr_nf4_rms(const void *x, const void *w, void *y, int32_t n, float eps,
+                void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Additive entries (no counterpart in the reference's header)               */
+/* ------------------------------------------------------------------------ */
+
+/* Library identification: "chr_nf4 sm_100a <build tag>". */
+const char *chr_nf4_version(void);
+
+/* Rows ids[0..n) of an NF4 table decoded to bf16( f32(LUT)*f32(scale) ),
+ * out bf16 [n, K]. ids: device int64. An id outside [0, M) yields a zero row
+ * and sets *status (device int32, optional) to 1. When position and valid_len
+ * are both non-null (device int64 / int32), *valid_len = *position + 1 is
+ * stored as well, which is what the greedy step needs before attention.
+ * Replaces the torch-op row decode gpu/host/embedding.py:74-107 (called from
+ * gpu/decodev2/embed.py:39-50). */
+int chr_nf4_embed_rows(const chr_nf4_dev_t *w, const void *ids, int32_t n,
+                       void *out, void *status, const void *position,
+                       void *valid_len, void *stream);
+
+/* Greedy pick and commit in one launch: next = argmax(logits[0..n)) (lowest
+ * index on ties, NaN counts as the maximum), then *next_token = next,
+ * *token = next, *position += 1, *finished |= (next == eos). logits bf16;
+ * next_token/token/position device int64; finished device uint8; token,
+ * position and finished may be NULL (pick only). scratch: 16 zero-initialised
+ * device bytes owned by the caller; the kernel leaves them zero again.
+ * Replaces the torch ops gpu/decodev2/step.py:182 and state.py:98-103. */
+int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_token,
+                        void *token, void *position, void *finished,
+                        int64_t eos, void *scratch, void *stream);
+
+/* Host-side NF4 codec, bit-exact with the reference's encoder/decoder
+ * (internal/nf4/nf4.go:46-121,129-185; gpu/tests/nf4_oracle.py:119-187).
+ * w: host float32 [M, K]; packed: host [M, K_pad/2]; scale: host binary16 bits
+ * [M, K_pad/64]. threads <= 0 uses every core. Returns 0, -1 (null), -3 (dims)
+ * or -8 (non-finite input). A group scale outside binary16's finite positive
+ * range is clamped as the Go writer does. */
+int chr_nf4_encode_f32(const float *w, int32_t M, int32_t K, uint8_t *packed,
+                       uint16_t *scale, int32_t threads);
+int chr_nf4_decode_f32(const uint8_t *packed, const uint16_t *scale, int32_t M,
+                       int32_t K, float *w, int32_t threads);
+
+/* The same encoder on the device, one warp per group: w device float32 [M, K],
+ * packed / scale device blobs of the shapes above, status optional device int32
+ * set to 1 when a non-finite weight is met. Bit-identical to the host encoder. */
+int chr_nf4_encode_dev(const float *w, int32_t M, int32_t K, uint8_t *packed,
+                       uint16_t *scale, int32_t *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,184 @@
+"""Resident executor on the GPU: greedy ids against the reference's float32 oracle
+(recorded in tests/golden), graph replay against eager, chunked prefill against
+token-by-token, packed embedding against dense, no allocation on the step path.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import model_ref as mr
+
+pytestmark = pytest.mark.gpu
+
+from gpu.decodev2 import (MEDIUM_LLAMA, TINY_INTERNLM, TINY_LLAMA, DecodeState, DecodeV2Loop,  # noqa: E402
+                          DeviceWeights, build, capture_greedy, consume_prompt, generate,
+                          greedy_decode, set_fuse_rms, teacher_force_token)
+
+CASES = {
+    "tiny_llama_s0_p1357": (TINY_LLAMA, 0),
+    "tiny_llama_s0_p456": (TINY_LLAMA, 0),
+    "tiny_internlm_s1_p1357": (TINY_INTERNLM, 1),
+    "medium_llama_s0_p1357": (MEDIUM_LLAMA, 0),
+}
+
+
+def session(spec, seed, **kw):
+    model = build(spec, seed)
+    weights = DeviceWeights.from_synth(model, "cuda", torch.bfloat16, **kw)
+    state = DecodeState.allocate(spec, weights.embed)
+    return model, state, weights
+
+
+def greedy_by_steps(state, weights, prompt, n_new):
+    for tok in prompt:
+        teacher_force_token(state, weights, tok)
+    out = [int(state.next_token.item())]
+    state.token.copy_(state.next_token)
+    for _ in range(n_new - 1):
+        if out[-1] == int(state.spec.eos_id):
+            break
+        greedy_decode(state, weights)
+        out.append(int(state.token.item()))
+    return out
+
+
+@pytest.mark.parametrize("tag", sorted(CASES))
+@pytest.mark.parametrize("fused", [True, False])
+def test_eager_greedy_ids_match_reference_oracle(golden, tag, fused):
+    g = golden("decodev2_oracle.npz")
+    spec, seed = CASES[tag]
+    _, state, weights = session(spec, seed)
+    set_fuse_rms(fused)
+    try:
+        got = greedy_by_steps(state, weights, g[tag + "_prompt"].tolist(), 8)
+    finally:
+        set_fuse_rms(True)
+    want = g[tag + "_greedy"].tolist()
+    assert got == want[: len(got)] and len(got) == len(want)
+
+
+@pytest.mark.parametrize("tag", sorted(CASES))
+def test_teacher_forced_logits_track_the_oracle(golden, tag):
+    g = golden("decodev2_oracle.npz")
+    spec, seed = CASES[tag]
+    _, state, weights = session(spec, seed)
+    want = g[tag + "_teacher"]
+    for i, tok in enumerate(g[tag + "_prompt"].tolist()):
+        teacher_force_token(state, weights, tok)
+        got = state.arena.logits[0].float().cpu().numpy()
+        assert int(state.next_token.item()) == int(want[i].argmax())
+        assert np.abs(got - want[i]).max() <= 0.05 * max(1.0, np.abs(want[i]).max())
+
+
+@pytest.mark.parametrize("spec,seed", [(TINY_LLAMA, 0), (TINY_INTERNLM, 1), (MEDIUM_LLAMA, 0)])
+def test_graph_replay_equals_eager(spec, seed):
+    prompt = [1, 3, 5, 7]
+    _, s_eager, w = session(spec, seed)
+    eager = greedy_by_steps(s_eager, w, prompt, 9)
+    _, s_graph, w2 = session(spec, seed)
+    graph = capture_greedy(s_graph, w2, warmup=2)
+    s_graph.reset()
+    for tok in prompt:
+        teacher_force_token(s_graph, w2, tok)
+    out = [int(s_graph.next_token.item())]
+    s_graph.token.copy_(s_graph.next_token)
+    for _ in range(8):
+        graph.replay()
+        out.append(int(s_graph.token.item()))
+    assert out == eager
+    assert int(s_graph.position.item()) == len(prompt) + 8
+    assert int(s_graph.valid_len.item()) == len(prompt) + 8
+
+
+def test_step_path_does_not_allocate():
+    _, state, weights = session(MEDIUM_LLAMA, 0)
+    for tok in (1, 3, 5):
+        teacher_force_token(state, weights, tok)
+    state.token.copy_(state.next_token)
+    greedy_decode(state, weights)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    for _ in range(4):
+        greedy_decode(state, weights)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
+
+
+def test_dirty_kv_tail_is_ignored():
+    _, clean, w = session(TINY_LLAMA, 0)
+    _, dirty, w2 = session(TINY_LLAMA, 0)
+    teacher_force_token(clean, w, 1)
+    teacher_force_token(dirty, w2, 1)
+    dirty.kv.k[:, -1].fill_(1.0e4)
+    dirty.kv.v[:, -1].fill_(1.0e4)
+    teacher_force_token(clean, w, 3)
+    teacher_force_token(dirty, w2, 3)
+    assert torch.equal(clean.arena.logits, dirty.arena.logits)
+
+
+@pytest.mark.parametrize("spec,seed", [(TINY_LLAMA, 0), (TINY_INTERNLM, 1), (MEDIUM_LLAMA, 0)])
+@pytest.mark.parametrize("chunk", [None, 3, 1])
+def test_chunked_prefill_tracks_token_by_token(spec, seed, chunk):
+    prompt = [1, 3, 5, 7, 2, 9, 11]
+    model, s_tok, w = session(spec, seed)
+    for tok in prompt:
+        teacher_force_token(s_tok, w, tok)
+    _, s_pre, w2 = session(spec, seed)
+    consume_prompt(s_pre, w2, prompt, chunk=chunk)
+    assert int(s_pre.position.item()) == len(prompt) == int(s_pre.valid_len.item())
+    want = mr.teacher_logits(model, prompt)[-1]
+    got = s_pre.arena.logits[0].float().cpu().numpy()
+    assert np.abs(got - want).max() <= 0.05 * max(1.0, np.abs(want).max())
+    assert int(s_pre.next_token.item()) == int(want.argmax())
+    # KV rows written by the GEMM prefill and by GEMV decode agree to bf16 noise
+    n = len(prompt)
+    dk = (s_pre.kv.k[:, :n].float() - s_tok.kv.k[:, :n].float()).abs().max().item()
+    assert dk <= 0.05 * max(1.0, s_tok.kv.k[:, :n].float().abs().max().item())
+
+
+def test_generate_and_loop_agree_with_oracle(golden):
+    g = golden("decodev2_oracle.npz")
+    tag = "medium_llama_s0_p1357"
+    model, state, weights = session(MEDIUM_LLAMA, 0)
+    prompt = g[tag + "_prompt"].tolist()
+    got = generate(state, weights, prompt, 8, ignore_eos=True)
+    want = mr.greedy_ids(model, prompt, 8)
+    assert got[: len(want)] == want
+    loop = DecodeV2Loop(state, weights)
+    assert loop.capture_graphs() == "decodev2", loop.graph_error
+    res = loop.generate(torch.tensor(prompt), 8)
+    assert res.tokens == got[: len(res.tokens)] and res.graph == "decodev2"
+    assert res.decode_steps == len(res.tokens) - 1 and res.prefill_ms > 0 and res.decode_ms > 0
+    win = loop.generate_device_window(prompt, 8)
+    assert win.tokens == got
+
+
+def test_packed_embed_equals_dense_of_same_codes():
+    import nf4_ref as o
+
+    model = build(MEDIUM_LLAMA, 0)
+    packed_w = DeviceWeights.from_synth(model, "cuda", packed_embed=True)
+    p, s = o.quantize(np.ascontiguousarray(model.embed, dtype=np.float32))
+    model.embed = o.dequantize(p, s, *model.embed.shape)
+    dense_w = DeviceWeights.from_synth(model, "cuda")
+    sp = DecodeState.allocate(MEDIUM_LLAMA, packed_w.embed)
+    sd = DecodeState.allocate(MEDIUM_LLAMA, dense_w.embed)
+    a = greedy_by_steps(sp, packed_w, [1, 3, 5, 7], 8)
+    b = greedy_by_steps(sd, dense_w, [1, 3, 5, 7], 8)
+    assert a == b and torch.equal(sp.arena.logits, sd.arena.logits)
+    assert int(sp.arena.status.item()) == 0
+
+
+def test_state_reset_and_registers():
+    _, state, weights = session(TINY_LLAMA, 0)
+    teacher_force_token(state, weights, 1)
+    assert int(state.position.item()) == 1 and int(state.valid_len.item()) == 1
+    state.reset()
+    assert int(state.position.item()) == 0 and int(state.valid_len.item()) == 0
+    with pytest.raises(ValueError):
+        consume_prompt(state, weights, list(range(17)))
+    with pytest.raises(RuntimeError):
+        DecodeState.allocate(TINY_LLAMA, torch.zeros(32, 64), device="cpu")

@@ -1,0 +1,422 @@
+"""CUDA kernels vs the CPU oracle, through the C ABI (ctypes) on the same inputs.
+
+Tolerance for GEMV / GEMM outputs is the one the path's specification states:
+max-abs-rel <= 1e-2, i.e. max|y - y_ref| / max|y_ref| (bf16 accumulate-order
+tolerance); the reference's own floor (max(0.05, half a bf16 ulp), absolute) is
+asserted as well. Integer / byte work (embedding rows, encoder, greedy pick) is
+bit-exact.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import model_ref as mr
+import nf4_ref as o
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+REL_TOL = 1e-2
+ABS_FLOOR = 0.05
+
+
+def t_u8(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def bf16_vec(rng, *shape, std=1.0):
+    a = (rng.standard_normal(shape) * std).astype(np.float32)
+    t = torch.from_numpy(a).to(torch.bfloat16)
+    return t.to(DEV), t.to(torch.float32).numpy()
+
+
+def blobs(m, k, seed, weight_like=True):
+    if weight_like:
+        rng = np.random.default_rng(seed)
+        w = (rng.standard_normal((m, k)) * 0.02).astype(np.float32)
+        p, s = o.quantize(w)
+    else:
+        p, s = o.random_blobs(m, k, seed, pad_garbage=True)
+    return p, s, t_u8(p), t_u8(s.view(np.uint16)).view(torch.float16)
+
+
+def assert_close(got: torch.Tensor, want: np.ndarray, what=""):
+    g = got.to(torch.float32).cpu().numpy().reshape(want.shape)
+    err = np.abs(g - want).max()
+    ref = np.abs(want).max()
+    half_ulp = 2.0 ** (np.floor(np.log2(max(ref, 1e-30))) - 8)
+    assert err <= REL_TOL * ref + 1e-30, f"{what}: max-abs-rel {err / ref:.3e} > {REL_TOL}"
+    assert err <= max(ABS_FLOOR, half_ulp), f"{what}: abs err {err:.4f}"
+    cos = float((g * want).sum() / (np.linalg.norm(g) * np.linalg.norm(want) + 1e-30))
+    assert cos > 0.999, f"{what}: cosine {cos}"
+
+
+GEMV_SHAPES = [
+    (2048, 2048), (256, 2048), (11008, 2048), (2048, 11008), (5120, 5120), (1024, 5120),
+    (5120, 13824), (6144, 16384), (5120, 27648), (130, 65), (7, 64), (1, 4096), (333, 1000),
+    (4096, 4096), (64, 32768),
+]
+
+
+@pytest.mark.parametrize("m,k", GEMV_SHAPES)
+def test_gemv_matches_oracle(m, k):
+    from gpu.nf4 import nf4_gemv
+
+    rng = np.random.default_rng(m * 31 + k)
+    p, s, pt, st = blobs(m, k, m + k, weight_like=(m * k > 100000))
+    xt, xf = bf16_vec(rng, k)
+    y = nf4_gemv(pt, st, xt, m, k, o.padded_k(k))
+    want = o.dequantize(p, s, m, k).astype(np.float64) @ xf.astype(np.float64)
+    assert y.shape == (m, 1) and y.dtype is torch.bfloat16
+    assert_close(y, want.astype(np.float32).reshape(m, 1), f"gemv {m}x{k}")
+    # repeat is bit-identical
+    y2 = nf4_gemv(pt, st, xt, m, k, o.padded_k(k))
+    assert torch.equal(y, y2)
+
+
+def test_gemv_pad_garbage_is_ignored():
+    from gpu.nf4 import nf4_gemv
+
+    m, k = 130, 65
+    p, s = o.random_blobs(m, k, 5, pad_garbage=True)
+    clean = o.split_nibbles(p)
+    clean[:, k:] = 7
+    p_clean = o.join_nibbles(clean)
+    xt, _ = bf16_vec(np.random.default_rng(0), k)
+    st = t_u8(s.view(np.uint16)).view(torch.float16)
+    a = nf4_gemv(t_u8(p), st, xt, m, k, 128)
+    b = nf4_gemv(t_u8(p_clean), st, xt, m, k, 128)
+    assert torch.equal(a, b)
+
+
+def test_gemv_residual_alias_and_out():
+    from gpu.nf4 import nf4_gemv
+
+    m, k = 2048, 2048
+    rng = np.random.default_rng(3)
+    p, s, pt, st = blobs(m, k, 77)
+    xt, xf = bf16_vec(rng, k)
+    rt, rf = bf16_vec(rng, m)
+    dest = rt.clone()
+    ret = nf4_gemv(pt, st, xt, m, k, k, dest, dest)
+    assert ret.data_ptr() == dest.data_ptr()
+    want = o.dequantize(p, s, m, k).astype(np.float64) @ xf.astype(np.float64) + rf
+    assert_close(dest, want.astype(np.float32), "gemv+residual")
+    # fused residual equals separate add of the un-rounded sum: check against plain gemv + add
+    plain = nf4_gemv(pt, st, xt, m, k, k).view(-1).float() + rt.float()
+    assert (dest.float() - plain).abs().max().item() <= 2 * 2.0 ** -8 * max(1.0, plain.abs().max().item())
+
+
+def test_gemv_fused_rms_equals_rms_then_gemv():
+    from gpu.nf4 import nf4_gemv, nf4_rms
+
+    m, k = 1024, 2048
+    rng = np.random.default_rng(5)
+    _, _, pt, st = blobs(m, k, 9)
+    xt, _ = bf16_vec(rng, k, std=3.0)
+    wt, _ = bf16_vec(rng, k, std=0.5)
+    h = torch.empty_like(xt)
+    nf4_rms(xt, wt, h, 1e-6)
+    a = nf4_gemv(pt, st, h, m, k, k)
+    b = nf4_gemv(pt, st, xt, m, k, k, rms_w=wt, rms_eps=1e-6)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("n", [64, 2048, 5120, 6144, 1000])
+def test_rms_matches_oracle(n):
+    from gpu.nf4 import nf4_rms
+
+    rng = np.random.default_rng(n)
+    xt, xf = bf16_vec(rng, n, std=2.0)
+    wt, wf = bf16_vec(rng, n, std=0.5)
+    y = torch.empty_like(xt)
+    nf4_rms(xt, wt, y, 1e-6)
+    want = mr.rms(xf[None], wf, 1e-6)[0]
+    g = y.float().cpu().numpy()
+    assert np.abs(g - want).max() <= 2.0 ** -8 * np.abs(want).max() + 1e-6
+    ref = torch.nn.functional.rms_norm(xt.float(), (n,), wt.float(), 1e-6)
+    assert (y.float() - ref).abs().max().item() <= 2.0 ** -7 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("mq,mkv,k,bias", [(2048, 256, 2048, True), (5120, 1024, 5120, True),
+                                            (64, 32, 64, False), (512, 128, 512, True),
+                                            (96, 40, 200, True)])
+def test_qkv_equals_three_gemvs(mq, mkv, k, bias):
+    from gpu.nf4 import nf4_gemv, nf4_qkv
+
+    rng = np.random.default_rng(mq + k)
+    kp = o.padded_k(k)
+    mats = [blobs(m, k, 100 + i, weight_like=False) for i, m in enumerate((mq, mkv, mkv))]
+    xt, xf = bf16_vec(rng, k)
+    biases = [bf16_vec(rng, m, std=0.02) if bias else (None, None) for m in (mq, mkv, mkv)]
+    outs = [torch.empty(m, dtype=torch.bfloat16, device=DEV) for m in (mq, mkv, mkv)]
+    nf4_qkv(mats[0][2], mats[0][3], mats[1][2], mats[1][3], mats[2][2], mats[2][3], xt, mq, mkv,
+            mkv, k, kp, *outs, biases[0][0], biases[1][0], biases[2][0])
+    for (p, s, pt, st), (bt, bf), out, m in zip(mats, biases, outs, (mq, mkv, mkv)):
+        want = o.dequantize(p, s, m, k).astype(np.float64) @ xf.astype(np.float64)
+        if bf is not None:
+            want = want + bf
+        assert_close(out, want.astype(np.float32), "qkv")
+        single = nf4_gemv(pt, st, xt, m, k, kp, add=bt).view(-1)
+        assert (out.float() - single.float()).abs().max().item() <= 1e-3 * max(
+            1.0, single.float().abs().max().item())
+
+
+@pytest.mark.parametrize("m,k", [(11008, 2048), (13824, 5120), (128, 64), (1024, 512),
+                                  (16384, 6144), (27648, 5120), (77, 200)])
+def test_swiglu_matches_oracle(m, k):
+    from gpu.nf4 import nf4_swiglu
+
+    rng = np.random.default_rng(m + 7 * k)
+    kp = o.padded_k(k)
+    pg, sg, pgt, sgt = blobs(m, k, 11, weight_like=(m * k > 100000))
+    pu, su, put, sut = blobs(m, k, 12, weight_like=(m * k > 100000))
+    xt, xf = bf16_vec(rng, k)
+    out = torch.empty(m, dtype=torch.bfloat16, device=DEV)
+    nf4_swiglu(pgt, sgt, put, sut, xt, m, k, kp, out)
+    g = o.dequantize(pg, sg, m, k).astype(np.float64) @ xf.astype(np.float64)
+    u = o.dequantize(pu, su, m, k).astype(np.float64) @ xf.astype(np.float64)
+    want = (g / (1.0 + np.exp(-g))) * u
+    assert_close(out, want.astype(np.float32), f"swiglu {m}x{k}")
+
+
+def _attn_case(n_q, n_kv, hd, max_seq, vl, seed):
+    rng = np.random.default_rng(seed)
+    qt, qf = bf16_vec(rng, n_q, hd)
+    kt, kf = bf16_vec(rng, max_seq, n_kv, hd)
+    vt, vf = bf16_vec(rng, max_seq, n_kv, hd)
+    return qt, qf, kt, kf, vt, vf
+
+
+class _Spec:
+    def __init__(self, n_q, n_kv, hd):
+        self.n_q, self.n_kv, self.head_dim = n_q, n_kv, hd
+        self.n_rep = n_q // n_kv
+        self.q_dim = n_q * hd
+        self.attn_scale = hd ** -0.5
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,max_seq,vl", [
+    (16, 2, 128, 2048, 513), (40, 8, 128, 1024, 1024), (48, 8, 128, 256, 1), (4, 2, 16, 16, 5),
+    (8, 2, 64, 32, 32), (8, 8, 256, 64, 40), (40, 8, 128, 512, 0), (12, 1, 128, 128, 77),
+])
+def test_attention_plain_matches_oracle(n_q, n_kv, hd, max_seq, vl):
+    from gpu.nf4 import ATTN_SPLIT, nf4_attn
+
+    qt, qf, kt, kf, vt, vf = _attn_case(n_q, n_kv, hd, max_seq, vl, n_q * hd + vl)
+    # poison the tail beyond valid_len: it must be ignored
+    kt[vl:] = 1.0e4
+    vt[vl:] = 1.0e4
+    out = torch.zeros(n_q * hd, dtype=torch.bfloat16, device=DEV)
+    valid = torch.tensor(vl, dtype=torch.int32, device=DEV)
+    nf4_attn(qt, kt, vt, out, valid, hd ** -0.5, None, ATTN_SPLIT)
+    if vl == 0:
+        assert float(out.float().abs().max()) == 0.0
+        return
+    want = mr.attend(qf[None], kf, vf, _Spec(n_q, n_kv, hd), vl)[0]
+    g = out.float().cpu().numpy()
+    assert np.abs(g - want).max() <= 0.02, np.abs(g - want).max()
+    # any split count gives the same answer within rounding
+    out2 = torch.zeros_like(out)
+    nf4_attn(qt, kt, vt, out2, valid, hd ** -0.5, None, 7)
+    assert (out.float() - out2.float()).abs().max().item() <= 0.01
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,max_seq,pos", [(16, 2, 128, 2048, 512), (40, 8, 128, 64, 0),
+                                                      (4, 2, 16, 16, 15), (8, 2, 64, 32, 9)])
+def test_attention_fused_rope_and_cache_write(n_q, n_kv, hd, max_seq, pos):
+    from gpu.nf4 import ATTN_SPLIT, nf4_attn, nf4_rope_kv
+
+    rng = np.random.default_rng(pos + hd)
+    qt, qf, kt, kf, vt, vf = _attn_case(n_q, n_kv, hd, max_seq, pos, 3 * pos + n_q)
+    kat, kaf = bf16_vec(rng, n_kv, hd)
+    vat, vaf = bf16_vec(rng, n_kv, hd)
+    cos, sin = mr.rope_tables(max_seq, hd, 1.0e6)
+    cos_t = torch.from_numpy(cos).to(DEV, torch.bfloat16)
+    sin_t = torch.from_numpy(sin).to(DEV, torch.bfloat16)
+    cos_b, sin_b = cos_t.float().cpu().numpy(), sin_t.float().cpu().numpy()
+    position = torch.tensor(pos, dtype=torch.int64, device=DEV)
+    valid = torch.tensor(pos + 1, dtype=torch.int32, device=DEV)
+    k_cache, v_cache = kt.clone(), vt.clone()
+    out = torch.zeros(n_q * hd, dtype=torch.bfloat16, device=DEV)
+    nf4_attn(qt, k_cache, v_cache, out, valid, hd ** -0.5, None, ATTN_SPLIT, kat, vat, cos_t, sin_t,
+             position)
+    q_rot = mr.rotate(qf[None], cos_b[pos:pos + 1], sin_b[pos:pos + 1])
+    k_rot = mr.rotate(kaf[None], cos_b[pos:pos + 1], sin_b[pos:pos + 1])[0]
+    kf2, vf2 = kf.copy(), vf.copy()
+    kf2[pos], vf2[pos] = k_rot, vaf
+    want = mr.attend(q_rot, kf2, vf2, _Spec(n_q, n_kv, hd), pos + 1)[0]
+    assert np.abs(out.float().cpu().numpy() - want).max() <= 0.02
+    # the cache row holds bf16(rotated k) and v; every other row is untouched
+    assert np.array_equal(o.bf16_bits(k_rot), k_cache[pos].view(torch.int16).cpu().numpy().view(np.uint16))
+    assert torch.equal(v_cache[pos], vat)
+    keep = [t for t in range(max_seq) if t != pos]
+    assert torch.equal(k_cache[keep], kt[keep]) and torch.equal(v_cache[keep], vt[keep])
+    # standalone rope_kv writes the same row and rotates q/k in place (bf16)
+    q2, k2, kc2, vc2 = qt.clone(), kat.clone(), kt.clone(), vt.clone()
+    nf4_rope_kv(q2, k2, vat, kc2, vc2, cos_t, sin_t, position)
+    assert torch.equal(kc2[pos], k_cache[pos]) and torch.equal(vc2[pos], vat)
+    assert np.array_equal(o.bf16_bits(q_rot[0]), q2.view(torch.int16).cpu().numpy().view(np.uint16))
+
+
+def test_embed_rows_bit_exact(golden):
+    from gpu.nf4 import nf4_embed_rows
+
+    g = golden("embed_rows.npz")
+    pt = t_u8(g["packed"])
+    st = t_u8(g["scale"]).view(torch.float16)
+    ids = torch.from_numpy(g["ids"]).to(DEV)
+    rows = nf4_embed_rows(pt, st, ids, 40, 200, 256)
+    assert np.array_equal(rows.view(torch.int16).cpu().numpy().view(np.uint16), g["rows_bf16_bits"])
+    # big table, K multiple of 8, against the oracle; bad id -> zero row + status
+    p, s, pt, st = blobs(5000, 6144, 21)
+    ids = torch.tensor([0, 4999, 17, 5000, -1], dtype=torch.int64, device=DEV)
+    status = torch.zeros((), dtype=torch.int32, device=DEV)
+    pos = torch.tensor(41, dtype=torch.int64, device=DEV)
+    vl = torch.zeros((), dtype=torch.int32, device=DEV)
+    rows = nf4_embed_rows(pt, st, ids, 5000, 6144, 6144, status=status, position=pos, valid_len=vl)
+    want = o.embed_rows(p, s, [0, 4999, 17], 6144)
+    got = rows.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got[:3], want)
+    assert (got[3:] == 0).all() and int(status.item()) == 1 and int(vl.item()) == 42
+
+
+def test_device_encoder_bit_exact():
+    from gpu.host.codec import encode_nf4, encode_nf4_device
+
+    rng = np.random.default_rng(8)
+    w = (rng.standard_normal((513, 1000)) * 0.02).astype(np.float32)
+    w[4] = 0
+    w[9, :64] = 1e6
+    w[10, :64] = 1e-9
+    u = np.concatenate([o.MID, np.nextafter(o.MID, np.float32(2)), np.nextafter(o.MID, np.float32(-2))])
+    w[11, : len(u)] = u
+    w[11, 63] = 1.0
+    p, s = encode_nf4(w)
+    pd, sd = encode_nf4_device(torch.from_numpy(w).to(DEV))
+    assert np.array_equal(pd.cpu().numpy(), p)
+    assert np.array_equal(sd.view(torch.int16).cpu().numpy().view(np.uint16), s.view(np.uint16))
+    with pytest.raises(ValueError):
+        encode_nf4_device(torch.full((2, 64), float("nan"), device=DEV))
+
+
+def test_pick_commit():
+    from gpu.nf4 import nf4_pick_commit
+
+    rng = np.random.default_rng(2)
+    for n in (32, 1000, 151936):
+        logits = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).to(DEV, torch.bfloat16)
+        logits[n // 3] = logits.max()          # a tie: lowest index must win
+        want = int(torch.argmax(logits.float()).item())
+        scratch = torch.zeros(16, dtype=torch.uint8, device=DEV)
+        nxt = torch.zeros((), dtype=torch.int64, device=DEV)
+        tok = torch.zeros((), dtype=torch.int64, device=DEV)
+        pos = torch.tensor(5, dtype=torch.int64, device=DEV)
+        fin = torch.zeros((), dtype=torch.uint8, device=DEV)
+        nf4_pick_commit(logits, nxt, scratch, tok, pos, fin, eos=want)
+        first = int((logits == logits.max()).nonzero()[0].item())
+        assert int(nxt.item()) == first == want
+        assert int(tok.item()) == want and int(pos.item()) == 6 and int(fin.item()) == 1
+        assert int(scratch.sum().item()) == 0
+        nf4_pick_commit(logits, nxt, scratch)   # pick only, scratch reusable
+        assert int(nxt.item()) == want and int(pos.item()) == 6
+    logits = torch.tensor([0.5, float("nan"), 3.0, -0.0, 0.0], dtype=torch.bfloat16, device=DEV)
+    nf4_pick_commit(logits, nxt, scratch)
+    assert int(nxt.item()) == 1
+    logits = torch.tensor([-1.0, -0.0, 0.0, -2.0], dtype=torch.bfloat16, device=DEV)
+    nf4_pick_commit(logits, nxt, scratch)
+    assert int(nxt.item()) == 1
+
+
+GEMM_CASES = [(128, 256, 16), (130, 65, 3), (2048, 2048, 32), (256, 2048, 9), (11008, 2048, 17),
+              (2048, 11008, 32), (4096, 4096, 32), (4096, 4096, 1), (300, 1000, 33), (512, 512, 64)]
+
+
+@pytest.mark.parametrize("m,k,n", GEMM_CASES)
+def test_gemm_matches_oracle(m, k, n):
+    from gpu.nf4 import PLAN_MAX_N, nf4_gemm
+
+    rng = np.random.default_rng(m + k + n)
+    p, s, pt, st = blobs(m, k, m * 3 + n, weight_like=(m * k > 100000))
+    xt, xf = bf16_vec(rng, k, n)
+    y = nf4_gemm(pt, st, xt, m, k, o.padded_k(k), max_n=PLAN_MAX_N if n > 32 else 32)
+    assert y.shape == (m, n) and y.dtype is torch.bfloat16
+    want = o.dequantize_bf16(p, s, m, k).astype(np.float64) @ xf.astype(np.float64)
+    assert_close(y, want.astype(np.float32), f"gemm {m}x{k}x{n}")
+    assert torch.equal(y, nf4_gemm(pt, st, xt, m, k, o.padded_k(k), max_n=PLAN_MAX_N if n > 32 else 32))
+
+
+def test_gemm_no_column_leak_and_pad_garbage():
+    from gpu.nf4 import nf4_gemm
+
+    m, k = 130, 65
+    p, s = o.random_blobs(m, k, 5, pad_garbage=True)
+    st = t_u8(s.view(np.uint16)).view(torch.float16)
+    clean = o.split_nibbles(p)
+    clean[:, k:] = 7
+    rng = np.random.default_rng(1)
+    x4, _ = bf16_vec(rng, k, 4)
+    x4[:, 3] = 1.0e30                       # a wild extra column must not leak into 0..2
+    x3 = x4[:, :3].contiguous()
+    y3 = nf4_gemm(t_u8(p), st, x3, m, k, 128)
+    y4 = nf4_gemm(t_u8(p), st, x4, m, k, 128)
+    assert torch.equal(y3, y4[:, :3].contiguous())
+    y3c = nf4_gemm(t_u8(o.join_nibbles(clean)), st, x3, m, k, 128)
+    assert torch.equal(y3, y3c)
+
+
+def test_gemm_split_k_agrees_within_one_ulp():
+    from gpu.nf4 import nf4_gemm, nf4_set_tuning
+
+    m, k, n = 512, 4096, 16
+    _, _, pt, st = blobs(m, k, 4)
+    xt, _ = bf16_vec(np.random.default_rng(6), k, n)
+    outs = []
+    try:
+        for split in (1, 2, 5, 64):
+            nf4_set_tuning(0, split, 0)
+            outs.append(nf4_gemm(pt, st, xt, m, k, k).float())
+    finally:
+        nf4_set_tuning(0, 0, 0)
+    for y in outs[1:]:
+        assert (y - outs[0]).abs().max().item() <= 2.0 ** -7 * outs[0].abs().max().item()
+
+
+def test_bad_arguments_are_rejected_without_launch():
+    from gpu.nf4 import nf4_gemm, nf4_gemv
+
+    _, _, pt, st = blobs(64, 128, 1, weight_like=False)
+    x = torch.zeros(128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="packed has"):
+        nf4_gemv(pt[:32], st, x, 64, 128, 128)
+    with pytest.raises(RuntimeError, match="scale has"):
+        nf4_gemm(pt, st[:10], x, 64, 128, 128)
+    with pytest.raises(RuntimeError, match="K_pad"):
+        nf4_gemv(pt, st, x, 64, 128, 192)
+    with pytest.raises(RuntimeError, match="bfloat16"):
+        nf4_gemm(pt, st, x.float(), 64, 128, 128)
+    with pytest.raises(RuntimeError, match=r"N=40"):
+        nf4_gemm(pt, st, torch.zeros((128, 40), dtype=torch.bfloat16, device=DEV), 64, 128, 128)
+    with pytest.raises(RuntimeError, match="out too small"):
+        nf4_gemv(pt, st, x, 64, 128, 128, out=torch.zeros(8, dtype=torch.bfloat16, device=DEV))
+    # misaligned x (offset by one element) is the C ABI's -5
+    xx = torch.zeros(129, dtype=torch.bfloat16, device=DEV)[1:]
+    with pytest.raises(RuntimeError, match=r"\(-5\)"):
+        nf4_gemv(pt, st, xx, 64, 128, 128)
+    torch.cuda.synchronize()
+
+
+def test_nan_does_not_bleed_across_rows():
+    from gpu.nf4 import nf4_gemv
+
+    m, k = 256, 512
+    _, s, pt, _ = blobs(m, k, 2, weight_like=False)
+    s = s.copy()
+    s.view(np.uint16)[7, 0] = 0x7E00         # NaN scale in row 7 only
+    st = t_u8(s.view(np.uint16)).view(torch.float16)
+    xt, _ = bf16_vec(np.random.default_rng(0), k)
+    y = nf4_gemv(pt, st, xt, m, k, k).view(-1).float()
+    assert torch.isnan(y[7]) and torch.isfinite(torch.cat([y[:7], y[8:]])).all()
