@@ -69,7 +69,10 @@ def test_teacher_forced_logits_track_the_oracle(golden, tag):
     for i, tok in enumerate(g[tag + "_prompt"].tolist()):
         teacher_force_token(state, weights, tok)
         got = state.arena.logits[0].float().cpu().numpy()
-        assert int(state.next_token.item()) == int(want[i].argmax())
+        top2 = np.sort(want[i])[-2:]
+        # logits are stored as bf16: only a margin above a few ulps pins the argmax
+        if top2[1] - top2[0] > 8 * 2.0 ** -8 * np.abs(want[i]).max():
+            assert int(state.next_token.item()) == int(want[i].argmax())
         assert np.abs(got - want[i]).max() <= 0.05 * max(1.0, np.abs(want[i]).max())
 
 
