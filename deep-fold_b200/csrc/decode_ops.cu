@@ -20,20 +20,9 @@ __global__ void __launch_bounds__(kRmsThreads) rms_kernel(const __nv_bfloat16 *_
                                                          const __nv_bfloat16 *__restrict__ w,
                                                          __nv_bfloat16 *__restrict__ y, int n,
                                                          float eps) {
-  __shared__ float red[kRmsThreads / 32];
   const int tid = threadIdx.x;
-  float acc = 0.f;
-  for (int i = tid; i < n; i += kRmsThreads) {
-    const float v = __bfloat162float(x[i]);
-    acc += v * v;
-  }
-  acc = warp_sum_xor(acc);
-  if ((tid & 31) == 0) red[tid >> 5] = acc;
-  __syncthreads();
-  float tot = 0.f;
-#pragma unroll
-  for (int i = 0; i < kRmsThreads / 32; ++i) tot += red[i];
-  const float s = rsqrtf(tot / static_cast<float>(n) + eps);
+  // same warp-level sum as the GEMV kernels' fused RMSNorm: identical scale bits
+  const float s = rsqrtf(warp_sumsq_bf16(x, n, tid & 31) / static_cast<float>(n) + eps);
   for (int i = tid; i < n; i += kRmsThreads) {
     y[i] = __float2bfloat16(__bfloat162float(w[i]) * __bfloat162float(x[i]) * s);
   }
@@ -83,12 +72,20 @@ constexpr int kAttnWarps = 4;
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr float kNegInit = -1.0e30f;
 
+// Arrival counters for the merge-by-last-CTA step: one per (kv head, head chunk).
+// Zero at load, and the last CTA of a group puts its counter back to zero, so a
+// launch leaves them as it found them. Launches of the attention kernel that
+// overlap on the device (different streams) would share them and must not.
+constexpr int kMaxAttnGroups = 1024;
+__device__ unsigned int g_attn_arrivals[kMaxAttnGroups];
+
 // P: bf16 pairs per lane (hd <= 64*P). H: query heads served by one CTA.
 template <int P, int H>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_cache,
-                  const __nv_bfloat16 *v_cache, float *__restrict__ m_s, float *__restrict__ l_s,
-                  float *__restrict__ o_s, const int32_t *__restrict__ valid_len,
+                  const __nv_bfloat16 *v_cache, __nv_bfloat16 *__restrict__ out,
+                  float *m_s, float *l_s, float *o_s,
+                  const int32_t *__restrict__ valid_len,
                   const __nv_bfloat16 *__restrict__ k_act, const __nv_bfloat16 *__restrict__ v_act,
                   const __nv_bfloat16 *__restrict__ cos, const __nv_bfloat16 *__restrict__ sin,
                   const int64_t *__restrict__ position, int n_q, int n_kv, int hd, int n_split,
@@ -99,6 +96,7 @@ attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_ca
   __shared__ float sm_m[kAttnWarps][H];
   __shared__ float sm_l[kAttnWarps][H];
   __shared__ float sm_o[kAttnWarps][H][64 * P];
+  __shared__ bool is_last;
 
   const int split = blockIdx.x;
   const int kvh = blockIdx.y;
@@ -188,37 +186,57 @@ attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_ca
     for (int e = 0; e < 2 * P; ++e) acc[h][e] = 0.f;
   }
 
-  for (int t = split + warp * n_split; t < vl; t += kAttnWarps * n_split) {
-    const bool cur = fuse_kv && t == pos;
+  // Token loop, one token ahead: the next row's K/V are in flight while this one
+  // is scored. Row t of this warp: split + warp*n_split + i*4*n_split.
+  const int t_step = kAttnWarps * n_split;
+  uint32_t kb[P], vb[P], kb_n[P], vb_n[P];
+  auto fetch = [&](int t, uint32_t (&kk)[P], uint32_t (&vv)[P]) {
     const size_t row = (static_cast<size_t>(t) * n_kv + kvh) * hd;
-    float kk[2 * P], vv[2 * P];
 #pragma unroll
     for (int p = 0; p < P; ++p) {
       const int d = 2 * lane + 64 * p;
-      if (d < hd) {
-        if (cur) {
-          kk[2 * p] = krot[d];
-          kk[2 * p + 1] = krot[d + 1];
-          vv[2 * p] = vcur[d];
-          vv[2 * p + 1] = vcur[d + 1];
-        } else {
-          const uint32_t kb = __ldg(reinterpret_cast<const uint32_t *>(k_cache + row + d));
-          const uint32_t vb = __ldg(reinterpret_cast<const uint32_t *>(v_cache + row + d));
-          kk[2 * p] = bf16_lo(kb);
-          kk[2 * p + 1] = bf16_hi(kb);
-          vv[2 * p] = bf16_lo(vb);
-          vv[2 * p + 1] = bf16_hi(vb);
-        }
+      const bool live = t < vl && d < hd;
+      kk[p] = live ? __ldg(reinterpret_cast<const uint32_t *>(k_cache + row + d)) : 0u;
+      vv[p] = live ? __ldg(reinterpret_cast<const uint32_t *>(v_cache + row + d)) : 0u;
+    }
+  };
+  int t = split + warp * n_split;
+  fetch(t, kb, vb);
+  for (; t < vl; t += t_step) {
+    fetch(t + t_step, kb_n, vb_n);
+    float kk[2 * P], vv[2 * P];
+    const bool cur = fuse_kv && t == pos;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      const int d = 2 * lane + 64 * p;
+      if (cur && d < hd) {
+        kk[2 * p] = krot[d];
+        kk[2 * p + 1] = krot[d + 1];
+        vv[2 * p] = vcur[d];
+        vv[2 * p + 1] = vcur[d + 1];
       } else {
-        kk[2 * p] = kk[2 * p + 1] = vv[2 * p] = vv[2 * p + 1] = 0.f;
+        kk[2 * p] = bf16_lo(kb[p]);
+        kk[2 * p + 1] = bf16_hi(kb[p]);
+        vv[2 * p] = bf16_lo(vb[p]);
+        vv[2 * p + 1] = bf16_hi(vb[p]);
       }
     }
+    float dots[H];
 #pragma unroll
     for (int h = 0; h < H; ++h) {
       float dot = 0.f;
 #pragma unroll
       for (int e = 0; e < 2 * P; ++e) dot = fmaf(qreg[h][e], kk[e], dot);
-      dot = warp_sum_xor(dot) * scale;
+      dots[h] = dot;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int h = 0; h < H; ++h) dots[h] += __shfl_xor_sync(0xffffffffu, dots[h], off);
+    }
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+      const float dot = dots[h] * scale;
       const float m2 = fmaxf(m[h], dot);
       const float alpha = __expf(m[h] - m2);
       const float ex = __expf(dot - m2);
@@ -226,6 +244,11 @@ attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_ca
 #pragma unroll
       for (int e = 0; e < 2 * P; ++e) acc[h][e] = acc[h][e] * alpha + ex * vv[e];
       m[h] = m2;
+    }
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      kb[p] = kb_n[p];
+      vb[p] = vb_n[p];
     }
   }
 
@@ -264,25 +287,36 @@ attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_ca
       l_s[slot] = ll;
     }
   }
-}
 
-__global__ void attn_merge_kernel(const float *__restrict__ m_s, const float *__restrict__ l_s,
-                                  const float *__restrict__ o_s, __nv_bfloat16 *__restrict__ out,
-                                  int hd, int n_split) {
-  const int head = blockIdx.x;
-  const float *mh = m_s + static_cast<size_t>(head) * n_split;
-  const float *lh = l_s + static_cast<size_t>(head) * n_split;
-  float m = kNegInit;
-  for (int s = 0; s < n_split; ++s) m = fmaxf(m, mh[s]);
-  float l = 0.f;
-  for (int s = 0; s < n_split; ++s) l += __expf(mh[s] - m) * lh[s];
-  __nv_bfloat16 *dst = out + static_cast<size_t>(head) * hd;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float o = 0.f;
+  // The last CTA of this (kv head, head chunk) to arrive merges the splits.
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned int *ctr = &g_attn_arrivals[(kvh * gridDim.z + blockIdx.z) % kMaxAttnGroups];
+    const unsigned int seen = atomicAdd(ctr, 1u);
+    is_last = seen == static_cast<unsigned int>(n_split) - 1u;
+    if (is_last) *ctr = 0u;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int i = tid; i < nh * hd; i += kAttnThreads) {
+    const int h = i / hd;
+    const int d = i - h * hd;
+    const size_t base = static_cast<size_t>(h_first + h) * n_split;
+    const volatile float *mh = m_s + base;
+    const volatile float *lh = l_s + base;
+    const volatile float *oh = o_s + base * hd + d;
+    float mm = kNegInit;
+    for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, mh[s]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll 8
     for (int s = 0; s < n_split; ++s) {
-      o += __expf(mh[s] - m) * o_s[(static_cast<size_t>(head) * n_split + s) * hd + d];
+      const float a = __expf(mh[s] - mm);
+      ll += a * lh[s];
+      oo += a * oh[static_cast<size_t>(s) * hd];
     }
-    dst[d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+    out[static_cast<size_t>(h_first + h) * hd + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
   }
 }
 
@@ -452,18 +486,19 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
   attn_split_kernel<PP, HH>                                                                    \
       <<<dim3(static_cast<unsigned>(n_split), static_cast<unsigned>(n_kv),                     \
               static_cast<unsigned>((n_rep + HH - 1) / HH)),                                   \
-         kAttnThreads, 0, st>>>(qp, kp, vp, m_s, l_s, o_s, vl, ka, va, cp, sp, pp, n_q, n_kv,  \
-                                hd, n_split, max_seq, scale)
+         kAttnThreads, 0, st>>>(qp, kp, vp, static_cast<__nv_bfloat16 *>(out), m_s, l_s, o_s,  \
+                                vl, ka, va, cp, sp, pp, n_q, n_kv, hd, n_split, max_seq, scale)
   if (hd <= 64) {
+    if (n_kv * ((n_rep + 7) / 8) > kMaxAttnGroups) return kDims;
     CHR_ATTN(1, 8);
   } else if (hd <= 128) {
+    if (n_kv * ((n_rep + 7) / 8) > kMaxAttnGroups) return kDims;
     CHR_ATTN(2, 8);
   } else {
+    if (n_kv * ((n_rep + 3) / 4) > kMaxAttnGroups) return kDims;
     CHR_ATTN(4, 4);
   }
 #undef CHR_ATTN
-  attn_merge_kernel<<<static_cast<unsigned>(n_q), 128, 0, st>>>(
-      m_s, l_s, o_s, static_cast<__nv_bfloat16 *>(out), hd, n_split);
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
 }
 

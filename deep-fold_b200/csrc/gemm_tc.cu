@@ -1,25 +1,438 @@
-// Tensor-core (tcgen05) NF4 GEMM for sm_100a -- placeholder until the kernel lands.
+// Tensor-core NF4 GEMM for sm_100a: TMA -> dequant warps -> tcgen05.mma -> TMEM.
+//
+// y[M,N] = bf16( sum_k bf16(LUT[code]*scale)[m,k] * x[k,n] ), N <= 64 per call.
+//
+// One CTA owns a 128-row tile of W and walks its share of the K tiles (BK = 64 =
+// one NF4 group) through a 4-stage ring:
+//   warp 0      TMA producer: the packed 128 x 32-byte code tile of each stage
+//               (cp.async.bulk.tensor.2d, no multicast) lands in shared memory.
+//   warps 2..5  one thread per W row: reads its 32 code bytes, multiplies the
+//               codebook value by the row's group scale in FP32, rounds once to
+//               bf16 (the reference's A operand, bit for bit) and stores the row
+//               into the stage's A tile in the K-major 128-byte-swizzled layout
+//               tcgen05 reads; the same threads lay the x tile out K-major as B.
+//   warp 1      one elected thread issues four tcgen05.mma (M=128, N=BN, K=16) per
+//               stage, accumulating in TMEM, and commits the stage back to the ring.
+//   warps 2..5  epilogue: tcgen05.ld of the 128 x BN FP32 accumulator, one row per
+//               thread, bf16 store (or FP32 split-K partial).
+// Group scales are fetched by the dequant threads with ordinary cached loads: the
+// scale matrix's row pitch (K_pad/32 bytes) is not a multiple of 16 bytes for
+// most shapes, which a TMA descriptor requires.
+//
+// Every mbarrier wait is bounded. A wait that runs out records a code in a device
+// status word (read with chr_nf4_gemm_status), the role stops issuing work, the
+// producer drains its copies in flight and the CTA still frees its TMEM.
+
+#include <cuda.h>
+
 #include "gemm_plan.h"
 #include "nf4_common.cuh"
 
 namespace chr {
 
+namespace {
+
+constexpr int tBM = 128;
+constexpr int tBK = 64;
+constexpr int tStages = 4;
+constexpr int tThreads = 192;
+constexpr int tRawBytes = tBM * (tBK / 2);      // 4096
+constexpr int tABytes = tBM * tBK * 2;          // 16384
+constexpr uint32_t kSpinLimit = 1u << 18;       // bounded mbarrier waits
+
+__device__ int g_gemm_status = 0;
+
+__host__ __device__ constexpr int b_bytes(int bn) { return bn * tBK * 2; }
+__host__ __device__ constexpr int stage_bytes(int bn) { return tRawBytes + tABytes + b_bytes(bn); }
+__host__ __device__ constexpr int smem_bytes(int bn) { return tStages * stage_bytes(bn) + 1024 /*align*/ + 256 /*barriers*/; }
+
+// ---- PTX wrappers -----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+// Returns false when the phase did not complete within the spin limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  // K-major, 128-byte swizzle: 8-row atoms of 1024 bytes (SBO), version 1.
+  uint64_t d = static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;            // leading byte offset (unused here)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;    // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;            // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;            // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const uint32_t a = __bfloat16_as_ushort(__float2bfloat16(lo));
+  const uint32_t b = __bfloat16_as_ushort(__float2bfloat16(hi));
+  return a | (b << 16);
+}
+
+// ---- kernel -------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(tThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap packed_map, const uint16_t *__restrict__ scale,
+               const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y,
+               float *__restrict__ partial, int M, int K, int K_pad, int N, int n_ktiles,
+               int tiles_per_split) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float lut[16];
+  __shared__ uint32_t tmem_slot;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int m0 = blockIdx.x * tBM;
+  const int kt0 = blockIdx.y * tiles_per_split;
+  const int kt1 = min(n_ktiles, kt0 + tiles_per_split);
+  const int n_local = kt1 - kt0;
+
+  // carve shared memory: stages (1024-byte aligned), then barriers
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  auto a_tile = [&](int s) { return base + s * tABytes; };
+  auto b_tile = [&](int s) { return base + tStages * tABytes + s * b_bytes(BN); };
+  auto raw_tile = [&](int s) { return base + tStages * (tABytes + b_bytes(BN)) + s * tRawBytes; };
+  const uint32_t bars = base + tStages * stage_bytes(BN);
+  auto raw_full = [&](int s) { return bars + 8 * s; };
+  auto ab_full = [&](int s) { return bars + 8 * (tStages + s); };
+  auto empty = [&](int s) { return bars + 8 * (2 * tStages + s); };
+  const uint32_t acc_full = bars + 8 * (3 * tStages);
+
+  if (tid < 16) lut[tid] = __uint_as_float(kLutBits[tid]);
+  if (tid == 0) {
+    for (int s = 0; s < tStages; ++s) {
+      mbar_init(raw_full(s), 1);
+      mbar_init(ab_full(s), 128);
+      mbar_init(empty(s), 1);
+    }
+    mbar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    constexpr uint32_t cols = BN < 32 ? 32 : BN;
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(cols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; i < n_local && ok; ++i) {
+        const int s = i % tStages;
+        if (i >= tStages) ok = mbar_wait(empty(s), ((i / tStages) - 1) & 1);
+        if (!ok) break;
+        mbar_expect_tx(raw_full(s), tRawBytes);
+        tma_load_2d(raw_tile(s), &packed_map, raw_full(s), (kt0 + i) * (tBK / 2), m0);
+        issued = i + 1;
+      }
+      if (!ok) {
+        atomicExch(&g_gemm_status, 1);
+        // drain: wait (bounded) for the copies this thread put in flight
+        for (int i = max(0, issued - tStages); i < issued; ++i) {
+          mbar_wait(raw_full(i % tStages), (i / tStages) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                 (static_cast<uint32_t>(BN >> 3) << 17) |
+                                 (static_cast<uint32_t>(tBM >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < n_local && ok; ++i) {
+        const int s = i % tStages;
+        ok = mbar_wait(ab_full(s), (i / tStages) & 1);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int k4 = 0; k4 < tBK / 16; ++k4) {
+          umma_bf16(tmem_d, umma_desc(a_tile(s) + k4 * 32), umma_desc(b_tile(s) + k4 * 32), idesc,
+                    (i > 0 || k4 > 0) ? 1u : 0u);
+        }
+        umma_commit(empty(s));
+      }
+      if (ok) {
+        umma_commit(acc_full);
+      } else {
+        atomicExch(&g_gemm_status, 2);
+      }
+    }
+  } else {
+    // ---------------- dequant + B fill (128 threads, one W row each) ----------------
+    const int r = tid - 64;                 // 0..127
+    const int grow = m0 + r;
+    const bool row_live = grow < M;
+    const int n_groups = K_pad / kGroup;
+    const uint32_t a_row_off = static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
+    const int sw = r & 7;
+    bool ok = true;
+    uint16_t s_bits = 0;
+    if (row_live && n_local > 0) {
+      s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt0);
+    }
+    for (int i = 0; i < n_local && ok; ++i) {
+      const int s = i % tStages;
+      const int kt = kt0 + i;
+      const float sc = row_live ? half_bits_to_float(s_bits) : 0.f;
+      if (row_live && i + 1 < n_local) {
+        s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt + 1);
+      }
+      if (i >= tStages) ok = mbar_wait(empty(s), ((i / tStages) - 1) & 1);
+      if (!ok) break;
+      ok = mbar_wait(raw_full(s), (i / tStages) & 1);
+      if (!ok) break;
+
+      // A: this row's 64 codes -> 64 bf16, eight 16-byte chunks, chunk c at c ^ (row & 7)
+      const uint32_t raw = raw_tile(s) + r * 32;
+      const int k_base = kt * tBK;
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        uint4 pk;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w)
+                     : "r"(raw + hlf * 16));
+        const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int c = hlf * 4 + c4;       // chunk of 8 codes
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t byte = (wv[c4] >> (8 * e)) & 0xFFu;
+            const int k = k_base + c * 8 + 2 * e;
+            float lo = lut[byte & 0xFu] * sc;
+            float hi = lut[byte >> 4] * sc;
+            if (k >= K) lo = 0.f;
+            if (k + 1 >= K) hi = 0.f;
+            o[e] = pack_bf16(lo, hi);
+          }
+          const uint32_t dst = a_tile(s) + a_row_off + static_cast<uint32_t>((c ^ sw) * 16);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o[0]), "r"(o[1]),
+                       "r"(o[2]), "r"(o[3])
+                       : "memory");
+        }
+      }
+
+      // B: x[k, n] (n contiguous in global) laid out K-major: row n, 64 k's, swizzled.
+      // thread r: k = r / 2 of this tile, columns (r & 1) * BN/2 .. + BN/2.
+      {
+        const int kk = r >> 1;
+        const int k = k_base + kk;
+        const int n_first = (r & 1) * (BN / 2);
+        const __nv_bfloat16 *src = x + static_cast<size_t>(k) * N;
+        const uint32_t chunk = static_cast<uint32_t>(kk >> 3);
+        const uint32_t within = static_cast<uint32_t>((kk & 7) * 2);
+#pragma unroll
+        for (int j = 0; j < BN / 2; ++j) {
+          const int n = n_first + j;
+          unsigned short v = 0;
+          if (k < K && n < N) v = __bfloat16_as_ushort(src[n]);
+          const uint32_t dst = b_tile(s) + static_cast<uint32_t>((n >> 3) * 1024 + (n & 7) * 128) +
+                               ((chunk ^ static_cast<uint32_t>(n & 7)) * 16) + within;
+          asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(v) : "memory");
+        }
+      }
+      // generic-proxy writes -> visible to the tensor core (async proxy), then signal
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(ab_full(s));
+    }
+    if (!ok) atomicExch(&g_gemm_status, 3);
+
+    // ---------------- epilogue ----------------
+    if (ok && n_local > 0) ok = mbar_wait(acc_full, 0);
+    if (!ok) atomicExch(&g_gemm_status, 4);
+    ok = __all_sync(0xffffffffu, ok);      // the TMEM loads below are warp-collective
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+      const int row = m0 + quad * 32 + lane;
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t v[16];
+        if (n_local > 0) {
+          tmem_ld16(tmem_d + (static_cast<uint32_t>(quad * 32) << 16) + c0, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = 0u;
+        }
+        if (row < M) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int n = c0 + e;
+            if (n < N) {
+              const float f = __uint_as_float(v[e]);
+              if (partial != nullptr) {
+                partial[(static_cast<size_t>(blockIdx.y) * M + row) * N + n] = f;
+              } else {
+                y[static_cast<size_t>(row) * N + n] = __float2bfloat16(f);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    constexpr uint32_t cols = BN < 32 ? 32 : BN;
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(cols));
+  }
+}
+
+// ---- host side -----------------------------------------------------------------
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                 const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                 const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      return static_cast<EncodeTiled>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiled>(p);
+  }();
+  return fn;
+}
+
+template <int BN>
+int launch(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y, int N, float *partial,
+           const chr_nf4_plan_t &p, cudaStream_t st) {
+  EncodeTiled enc = encode_fn();
+  if (enc == nullptr) return kLaunch;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(w.K_pad / 2), static_cast<cuuint64_t>(w.M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(w.K_pad / 2)};
+  const cuuint32_t box[2] = {tBK / 2, tBM};
+  const cuuint32_t elem[2] = {1, 1};
+  if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w.packed), dims, strides,
+          box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    return kLaunch;
+  }
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem_bytes(BN)) != cudaSuccess) {
+      return kLaunch;
+    }
+    attr_done = true;
+  }
+  const dim3 grid(static_cast<unsigned>(p.grid_x), static_cast<unsigned>(p.grid_y));
+  gemm_tc_kernel<BN><<<grid, tThreads, smem_bytes(BN), st>>>(
+      map, w.scale, x, y, partial, w.M, w.K, w.K_pad, N, p.n_ktiles, p.tiles_per_split);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+}
+
+int bn_for(int N) { return N <= 16 ? 16 : (N <= 32 ? 32 : 64); }
+
+}  // namespace
+
 TileShape tc_tile_shape(int N) {
-  (void)N;
-  return TileShape{128, 64, 192, 0};
+  return TileShape{tBM, tBK, tThreads, smem_bytes(bn_for(N))};
 }
 
 bool tc_supported(int M, int K_pad, int N) {
   (void)M;
-  (void)K_pad;
-  (void)N;
-  return false;
+  // the packed row pitch must be a multiple of 16 bytes for the TMA descriptor
+  return N >= 1 && N <= 64 && (K_pad / 2) % 16 == 0;
 }
 
 int launch_gemm_tc(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y, int N,
                    float *partial, const chr_nf4_plan_t &p, cudaStream_t st) {
-  (void)w; (void)x; (void)y; (void)N; (void)partial; (void)p; (void)st;
-  return kLaunch;
+  switch (bn_for(N)) {
+    case 16: return launch<16>(w, x, y, N, partial, p, st);
+    case 32: return launch<32>(w, x, y, N, partial, p, st);
+    default: return launch<64>(w, x, y, N, partial, p, st);
+  }
 }
 
 }  // namespace chr
+
+// Reads and clears the GEMM status word: 0 = every bounded wait completed; 1..4 =
+// producer / MMA issuer / dequant / epilogue gave up on a wait. Synchronises the device.
+extern "C" int chr_nf4_gemm_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, chr::g_gemm_status, sizeof(int)) != cudaSuccess) return chr::kLaunch;
+  if (v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(chr::g_gemm_status, &zero, sizeof(int));
+  }
+  return v;
+}

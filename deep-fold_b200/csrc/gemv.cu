@@ -30,7 +30,10 @@ namespace chr {
 namespace {
 
 constexpr int kChunk = 1024;        // k per warp-wide 16-byte load
-constexpr int kMaxWarps = 16;
+#ifndef CHR_GEMV_MAX_WARPS
+#define CHR_GEMV_MAX_WARPS 16
+#endif
+constexpr int kMaxWarps = CHR_GEMV_MAX_WARPS;
 constexpr int kTabBytes = 65536;    // 256 byte values x 32 lanes x float2
 constexpr int kHeadBytes = 16384;   // partial sums + RMS scratch in front of the table
 constexpr int kSmemBytes = kHeadBytes + 2 * kTabBytes;  // room to place the table on a 64 KiB boundary
@@ -92,27 +95,65 @@ __device__ __forceinline__ int reduced_row_of_lane(int lane) {
   return 0;
 }
 
-// Unscaled dot of 32 codes (one uint4) with the lane's 32 x values.
-__device__ __forceinline__ float dot32(const uint4 pk, const float2 (&xr)[16], uint32_t tab_lane) {
-  float2 acc0 = make_float2(0.f, 0.f);
-  float2 acc1 = make_float2(0.f, 0.f);
-  const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    // selector 0x76b4: byte0 <- tab_lane.byte0, byte1 <- code byte b, bytes 2,3 <- tab_lane.
-    const uint32_t a0 = __byte_perm(w[i], tab_lane, 0x7604);
-    const uint32_t a1 = __byte_perm(w[i], tab_lane, 0x7614);
-    const uint32_t a2 = __byte_perm(w[i], tab_lane, 0x7624);
-    const uint32_t a3 = __byte_perm(w[i], tab_lane, 0x7634);
-    acc0 = ffma2(lds_f2(a0), xr[4 * i + 0], acc0);
-    acc1 = ffma2(lds_f2(a1), xr[4 * i + 1], acc1);
-    acc0 = ffma2(lds_f2(a2), xr[4 * i + 2], acc0);
-    acc1 = ffma2(lds_f2(a3), xr[4 * i + 3], acc1);
+// Four code bytes (8 weights): four byte-permutes build the table addresses
+// (byte0 <- tab_lane.byte0, byte1 <- code byte, bytes 2,3 <- tab_lane), four 8-byte
+// shared loads fetch the (low, high) codebook pairs, four packed FMAs accumulate.
+// One asm statement, so nothing is scheduled in between by the front end.
+template <bool FIRST>
+__device__ __forceinline__ void dot8(uint32_t w, uint32_t tab_lane, f32x2_t x0, f32x2_t x1,
+                                     f32x2_t x2, f32x2_t x3, f32x2_t &acc0, f32x2_t &acc1) {
+  if constexpr (FIRST) {
+    asm volatile(
+        "{\n\t.reg .b32 a0, a1, a2, a3;\n\t.reg .b64 t0, t1, t2, t3;\n\t"
+        "prmt.b32 a0, %2, %3, 0x7604;\n\t"
+        "prmt.b32 a1, %2, %3, 0x7614;\n\t"
+        "prmt.b32 a2, %2, %3, 0x7624;\n\t"
+        "prmt.b32 a3, %2, %3, 0x7634;\n\t"
+        "ld.shared.b64 t0, [a0];\n\t"
+        "ld.shared.b64 t1, [a1];\n\t"
+        "ld.shared.b64 t2, [a2];\n\t"
+        "ld.shared.b64 t3, [a3];\n\t"
+        "mul.rn.f32x2 %0, t0, %4;\n\t"
+        "mul.rn.f32x2 %1, t1, %5;\n\t"
+        "fma.rn.f32x2 %0, t2, %6, %0;\n\t"
+        "fma.rn.f32x2 %1, t3, %7, %1;\n\t}"
+        : "=&l"(acc0), "=&l"(acc1)
+        : "r"(w), "r"(tab_lane), "l"(x0), "l"(x1), "l"(x2), "l"(x3));
+  } else {
+    asm volatile(
+        "{\n\t.reg .b32 a0, a1, a2, a3;\n\t.reg .b64 t0, t1, t2, t3;\n\t"
+        "prmt.b32 a0, %2, %3, 0x7604;\n\t"
+        "prmt.b32 a1, %2, %3, 0x7614;\n\t"
+        "prmt.b32 a2, %2, %3, 0x7624;\n\t"
+        "prmt.b32 a3, %2, %3, 0x7634;\n\t"
+        "ld.shared.b64 t0, [a0];\n\t"
+        "ld.shared.b64 t1, [a1];\n\t"
+        "ld.shared.b64 t2, [a2];\n\t"
+        "ld.shared.b64 t3, [a3];\n\t"
+        "fma.rn.f32x2 %0, t0, %4, %0;\n\t"
+        "fma.rn.f32x2 %1, t1, %5, %1;\n\t"
+        "fma.rn.f32x2 %0, t2, %6, %0;\n\t"
+        "fma.rn.f32x2 %1, t3, %7, %1;\n\t}"
+        : "+l"(acc0), "+l"(acc1)
+        : "r"(w), "r"(tab_lane), "l"(x0), "l"(x1), "l"(x2), "l"(x3));
   }
-  return (acc0.x + acc1.x) + (acc0.y + acc1.y);
 }
 
-// MODE 0: plain / fused q,k,v rows (+ residual or bias). MODE 1: SwiGLU (gate, up).
+// Unscaled dot of 32 codes (one uint4) with the lane's 32 x values (16 packed pairs).
+__device__ __forceinline__ float dot32(const uint4 pk, const f32x2_t (&xr)[16], uint32_t tab_lane) {
+  f32x2_t acc0, acc1;
+  dot8<true>(pk.x, tab_lane, xr[0], xr[1], xr[2], xr[3], acc0, acc1);
+  dot8<false>(pk.y, tab_lane, xr[4], xr[5], xr[6], xr[7], acc0, acc1);
+  dot8<false>(pk.z, tab_lane, xr[8], xr[9], xr[10], xr[11], acc0, acc1);
+  dot8<false>(pk.w, tab_lane, xr[12], xr[13], xr[14], xr[15], acc0, acc1);
+  float e0, o0, e1, o1;
+  unpack_f32x2(acc0, e0, o0);
+  unpack_f32x2(acc1, e1, o1);
+  return (e0 + e1) + (o0 + o1);
+}
+
+// MODE 0: one matrix (+ residual). MODE 1: SwiGLU (gate, up). MODE 2: fused q, k, v
+// rows in one row space (+ bias each).
 template <int R, int C, int MODE>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1)
 nf4_gemv_kernel(const GemvArgs a) {
@@ -121,113 +162,56 @@ nf4_gemv_kernel(const GemvArgs a) {
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int n_warps = blockDim.x >> 5;
   const int s = warp % a.S;
   const int g = warp / a.S;
 
-  float *part = reinterpret_cast<float *>(smem);                  // [2][S][G*RW]
-  float *red = reinterpret_cast<float *>(smem + kHeadBytes - 128); // RMS scratch
-
-  // Table on a 64 KiB boundary of the shared window so that a byte-permute can
-  // splice the code byte into address bits 8..15.
-  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-  const uint32_t tab_base = (smem_base + kHeadBytes + 0xFFFFu) & ~0xFFFFu;
-  {
-    // entry (b, l) at tab_base + b*256 + l*8
-    for (int i = tid; i < 256 * 32; i += blockDim.x) {
-      const int b = i >> 5;
-      const float lo = __uint_as_float(kLutBits[b & 15]);
-      const float hi = __uint_as_float(kLutBits[b >> 4]);
-      const uint32_t addr = tab_base + static_cast<uint32_t>(i) * 8u;
-      asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(lo), "f"(hi));
-    }
-  }
-  const uint32_t tab_lane = tab_base + static_cast<uint32_t>(lane) * 8u;
-
-  // Optional fused RMSNorm: inv = rsqrt(mean(x^2) + eps) over all K.
-  float inv = 1.f;
-  if (a.rms_w != nullptr) {
-    float acc = 0.f;
-    for (int i = tid; i < a.K; i += blockDim.x) {
-      const float v = __bfloat162float(a.x[i]);
-      acc += v * v;
-    }
-    acc = warp_sum_xor(acc);
-    if (lane == 0) red[warp] = acc;
-    __syncthreads();
-    float tot = 0.f;
-    for (int w = 0; w < n_warps; ++w) tot += red[w];
-    inv = rsqrtf(tot / static_cast<float>(a.K) + a.rms_eps);
-  }
-
-  // The lane's x values for its K slice, zero at and beyond K.
-  float2 xr[C][16];
-  bool chunk_live[C];
-#pragma unroll
-  for (int j = 0; j < C; ++j) {
-    const int k0 = (s * C + j) * kChunk + lane * 32;
-    chunk_live[j] = k0 < a.K_pad;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int k = k0 + q * 8;
-      uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-      if (k + 8 <= a.K) {
-        xv = *reinterpret_cast<const uint4 *>(a.x + k);
-      } else if (k < a.K) {
-        __nv_bfloat16 tmp[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) tmp[e] = (k + e < a.K) ? a.x[k + e] : __float2bfloat16(0.f);
-        xv = *reinterpret_cast<const uint4 *>(tmp);
-      }
-      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float lo = bf16_lo(xw[e]);
-        float hi = bf16_hi(xw[e]);
-        if (a.rms_w != nullptr) {
-          const int kk = k + 2 * e;
-          const float w0 = kk < a.K ? __bfloat162float(a.rms_w[kk]) : 0.f;
-          const float w1 = kk + 1 < a.K ? __bfloat162float(a.rms_w[kk + 1]) : 0.f;
-          lo = __bfloat162float(__float2bfloat16(w0 * lo * inv));
-          hi = __bfloat162float(__float2bfloat16(w1 * hi * inv));
-        }
-        xr[j][q * 4 + e] = make_float2(lo, hi);
-      }
-    }
-  }
-  __syncthreads();  // table and RMS scratch are ready
+  float *part = reinterpret_cast<float *>(smem);  // [2][S][G*RW]
 
   const int rt = a.G * R;                 // unit rows per tile
   const int half_stride = a.K_pad >> 1;   // bytes per packed row
   const int n_groups = a.K_pad / kGroup;
+  const int last_row = a.n_rows - 1;
+  const int last_tile = a.n_tiles - 1;
+  bool chunk_live[C];
+#pragma unroll
+  for (int j = 0; j < C; ++j) chunk_live[j] = (s * C + j) * kChunk + lane * 32 < a.K_pad;
+  // this lane's byte / scale offset inside any row (chunk j adds j*512 bytes, j*16 scales)
+  const size_t lane_pk = static_cast<size_t>(s) * C * (kChunk / 2) + static_cast<size_t>(lane) * 16;
+  const size_t lane_sc = static_cast<size_t>(s) * C * (kChunk / kGroup) + static_cast<size_t>(lane >> 1);
 
   uint4 cur[RW][C], nxt[RW][C];
   uint16_t cur_s[RW][C], nxt_s[RW][C];
 
+  // Rows and tiles past the end are clamped to the last one: every load stays in
+  // bounds without a branch, the duplicates are dropped at the store.
   auto issue = [&](int tile, uint4 (&pk)[RW][C], uint16_t (&sc)[RW][C]) {
-    const int row0 = tile * rt + g * R;
+    const int row0 = min(tile, last_tile) * rt + g * R;
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
-      const int unit = row0 + (MODE == 1 ? (i >> 1) : i);
-      const uint8_t *pbase;
-      const uint16_t *sbase;
-      int local = unit;
+      const int unit = min(row0 + (MODE == 1 ? (i >> 1) : i), last_row);
+      const uint8_t *pr;
+      const uint16_t *sr;
       if constexpr (MODE == 1) {
-        pbase = (i & 1) ? a.packed[1] : a.packed[0];
-        sbase = (i & 1) ? a.scale[1] : a.scale[0];
+        pr = ((i & 1) ? a.packed[1] : a.packed[0]) + static_cast<size_t>(unit) * half_stride;
+        sr = ((i & 1) ? a.scale[1] : a.scale[0]) + static_cast<size_t>(unit) * n_groups;
+      } else if constexpr (MODE == 0) {
+        pr = a.packed[0] + static_cast<size_t>(unit) * half_stride;
+        sr = a.scale[0] + static_cast<size_t>(unit) * n_groups;
       } else {
         const int m = (unit >= a.rows_end[0]) + (unit >= a.rows_end[1]);
-        pbase = m == 0 ? a.packed[0] : (m == 1 ? a.packed[1] : a.packed[2]);
-        sbase = m == 0 ? a.scale[0] : (m == 1 ? a.scale[1] : a.scale[2]);
-        local = unit - (m == 0 ? 0 : (m == 1 ? a.rows_end[0] : a.rows_end[1]));
+        const int local = unit - (m == 0 ? 0 : (m == 1 ? a.rows_end[0] : a.rows_end[1]));
+        pr = (m == 0 ? a.packed[0] : (m == 1 ? a.packed[1] : a.packed[2])) +
+             static_cast<size_t>(local) * half_stride;
+        sr = (m == 0 ? a.scale[0] : (m == 1 ? a.scale[1] : a.scale[2])) +
+             static_cast<size_t>(local) * n_groups;
       }
-      const bool row_live = tile < a.n_tiles && unit < a.n_rows;
+      pr += lane_pk;
+      sr += lane_sc;
 #pragma unroll
       for (int j = 0; j < C; ++j) {
-        const int k0 = (s * C + j) * kChunk + lane * 32;
-        if (row_live && chunk_live[j]) {
-          pk[i][j] = ld_stream16(pbase + static_cast<size_t>(local) * half_stride + (k0 >> 1));
-          sc[i][j] = ld_stream_u16(sbase + static_cast<size_t>(local) * n_groups + (k0 >> 6));
+        if (chunk_live[j]) {
+          pk[i][j] = ld_stream16(pr + j * (kChunk / 2));
+          sc[i][j] = ld_stream_u16(sr + j * (kChunk / kGroup));
         } else {
           pk[i][j] = make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
           sc[i][j] = 0;
@@ -236,51 +220,121 @@ nf4_gemv_kernel(const GemvArgs a) {
     }
   };
 
+  // The first tile's weights depend on nothing this kernel computes: put them in
+  // flight before the table is built and x is read.
   int tile = blockIdx.x;
   issue(tile, cur, cur_s);
-  int buf = 0;
-  for (; tile < a.n_tiles; tile += gridDim.x) {
-    issue(tile + gridDim.x, nxt, nxt_s);
 
+  // Table on a 64 KiB boundary of the shared window so that a byte-permute can
+  // splice the code byte into address bits 8..15. Entry (b, l) at b*256 + l*8.
+  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const uint32_t tab_base = (smem_base + kHeadBytes + 0xFFFFu) & ~0xFFFFu;
+  for (int i = tid; i < 256 * 32; i += blockDim.x) {
+    const int b = i >> 5;
+    const float lo = __uint_as_float(kLutBits[b & 15]);
+    const float hi = __uint_as_float(kLutBits[b >> 4]);
+    const uint32_t addr = tab_base + static_cast<uint32_t>(i) * 8u;
+    asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(lo), "f"(hi));
+  }
+  const uint32_t tab_lane = tab_base + static_cast<uint32_t>(lane) * 8u;
+
+  // Optional fused RMSNorm: every warp derives the same scale on its own.
+  float inv = 1.f;
+  if (a.rms_w != nullptr) {
+    inv = rsqrtf(warp_sumsq_bf16(a.x, a.K, lane) / static_cast<float>(a.K) + a.rms_eps);
+  }
+
+  // The lane's x values for its K slice as packed (even, odd) pairs, zero at and beyond K.
+  f32x2_t xr[C][16];
+#pragma unroll
+  for (int j = 0; j < C; ++j) {
+    const int k0 = (s * C + j) * kChunk + lane * 32;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int k = k0 + q * 8;
+      uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+      uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+      if (k + 8 <= a.K) {
+        xv = __ldg(reinterpret_cast<const uint4 *>(a.x + k));
+        if (a.rms_w != nullptr) wv = __ldg(reinterpret_cast<const uint4 *>(a.rms_w + k));
+      } else if (k < a.K) {
+        __nv_bfloat16 tx[8], tw[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const bool in = k + e < a.K;
+          tx[e] = in ? a.x[k + e] : __float2bfloat16(0.f);
+          tw[e] = (in && a.rms_w != nullptr) ? a.rms_w[k + e] : __float2bfloat16(0.f);
+        }
+        xv = *reinterpret_cast<const uint4 *>(tx);
+        wv = *reinterpret_cast<const uint4 *>(tw);
+      }
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float lo = bf16_lo(xw[e]);
+        float hi = bf16_hi(xw[e]);
+        if (a.rms_w != nullptr) {
+          lo = __bfloat162float(__float2bfloat16(bf16_lo(ww[e]) * lo * inv));
+          hi = __bfloat162float(__float2bfloat16(bf16_hi(ww[e]) * hi * inv));
+        }
+        xr[j][q * 4 + e] = pack_f32x2(lo, hi);
+      }
+    }
+  }
+  __syncthreads();  // table is ready
+
+  // Output routing of a unit row (MODE 2 only needs the three-way split).
+  auto store_plain = [&](int unit, float v) {
+    if (unit >= a.n_rows) return;
+    if constexpr (MODE == 2) {
+      const int m = (unit >= a.rows_end[0]) + (unit >= a.rows_end[1]);
+      const int local = unit - (m == 0 ? 0 : (m == 1 ? a.rows_end[0] : a.rows_end[1]));
+      const __nv_bfloat16 *ex = m == 0 ? a.extra[0] : (m == 1 ? a.extra[1] : a.extra[2]);
+      __nv_bfloat16 *yo = m == 0 ? a.y[0] : (m == 1 ? a.y[1] : a.y[2]);
+      if (ex != nullptr) v += __bfloat162float(ex[local]);
+      yo[local] = __float2bfloat16(v);
+    } else {
+      if (a.extra[0] != nullptr) v += __bfloat162float(a.extra[0][unit]);
+      a.y[0][unit] = __float2bfloat16(v);
+    }
+  };
+
+  int buf = 0;
+  auto process = [&](int tile, const uint4 (&pk)[RW][C], const uint16_t (&sc)[RW][C]) {
     float sum[RW];
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
       sum[i] = 0.f;
 #pragma unroll
       for (int j = 0; j < C; ++j) {
-        const float d = dot32(cur[i][j], xr[j], tab_lane);
-        sum[i] = fmaf(half_bits_to_float(cur_s[i][j]), d, sum[i]);
+        const float d = dot32(pk[i][j], xr[j], tab_lane);
+        sum[i] = fmaf(half_bits_to_float(sc[i][j]), d, sum[i]);
       }
     }
     const float tot = warp_reduce_rows<RW>(sum, lane);
     const int my = reduced_row_of_lane<RW>(lane);  // weight-row index this lane holds
-    const int lanes_per = 32 / RW;
+    constexpr int lanes_per = 32 / RW;
 
     if (a.S > 1) {
       float *pb = part + buf * (kMaxWarps * 8);
       if ((lane & (lanes_per - 1)) == 0) pb[s * (a.G * RW) + g * RW + my] = tot;
       __syncthreads();
-      const int n_out = rt;  // unit rows in this tile
-      if (tid < n_out) {
+      if (tid < rt) {
         const int unit = tile * rt + tid;
-        if (unit < a.n_rows) {
-          if constexpr (MODE == 1) {
-            float gsum = 0.f, usum = 0.f;
-            for (int q = 0; q < a.S; ++q) {
-              gsum += pb[q * (a.G * RW) + 2 * tid];
-              usum += pb[q * (a.G * RW) + 2 * tid + 1];
-            }
-            a.y[0][unit] = __float2bfloat16((gsum / (1.f + expf(-gsum))) * usum);
-          } else {
-            float v = 0.f;
-            for (int q = 0; q < a.S; ++q) v += pb[q * (a.G * RW) + tid];
-            const int m = (unit >= a.rows_end[0]) + (unit >= a.rows_end[1]);
-            const int local = unit - (m == 0 ? 0 : (m == 1 ? a.rows_end[0] : a.rows_end[1]));
-            const __nv_bfloat16 *ex = m == 0 ? a.extra[0] : (m == 1 ? a.extra[1] : a.extra[2]);
-            __nv_bfloat16 *yo = m == 0 ? a.y[0] : (m == 1 ? a.y[1] : a.y[2]);
-            if (ex != nullptr) v += __bfloat162float(ex[local]);
-            yo[local] = __float2bfloat16(v);
+        if constexpr (MODE == 1) {
+          float gsum = 0.f, usum = 0.f;
+          for (int q = 0; q < a.S; ++q) {
+            gsum += pb[q * (a.G * RW) + 2 * tid];
+            usum += pb[q * (a.G * RW) + 2 * tid + 1];
           }
+          if (unit < a.n_rows) {
+            a.y[0][unit] = __float2bfloat16((gsum / (1.f + expf(-gsum))) * usum);
+          }
+        } else {
+          float v = 0.f;
+          for (int q = 0; q < a.S; ++q) v += pb[q * (a.G * RW) + tid];
+          store_plain(unit, v);
         }
       }
       buf ^= 1;
@@ -295,29 +349,22 @@ nf4_gemv_kernel(const GemvArgs a) {
           }
         }
       } else {
-        if ((lane & (lanes_per - 1)) == 0) {
-          const int unit = tile * rt + g * R + my;
-          if (unit < a.n_rows) {
-            const int m = (unit >= a.rows_end[0]) + (unit >= a.rows_end[1]);
-            const int local = unit - (m == 0 ? 0 : (m == 1 ? a.rows_end[0] : a.rows_end[1]));
-            const __nv_bfloat16 *ex = m == 0 ? a.extra[0] : (m == 1 ? a.extra[1] : a.extra[2]);
-            __nv_bfloat16 *yo = m == 0 ? a.y[0] : (m == 1 ? a.y[1] : a.y[2]);
-            float v = tot;
-            if (ex != nullptr) v += __bfloat162float(ex[local]);
-            yo[local] = __float2bfloat16(v);
-          }
-        }
+        if ((lane & (lanes_per - 1)) == 0) store_plain(tile * rt + g * R + my, tot);
       }
     }
+  };
 
-#pragma unroll
-    for (int i = 0; i < RW; ++i) {
-#pragma unroll
-      for (int j = 0; j < C; ++j) {
-        cur[i][j] = nxt[i][j];
-        cur_s[i][j] = nxt_s[i][j];
-      }
-    }
+  // Two register buffers alternate: the next tile's loads are in flight while the
+  // current tile is reduced.
+  const int stride = gridDim.x;
+  while (tile < a.n_tiles) {
+    issue(tile + stride, nxt, nxt_s);
+    process(tile, cur, cur_s);
+    tile += stride;
+    if (tile >= a.n_tiles) break;
+    issue(tile + stride, cur, cur_s);
+    process(tile, nxt, nxt_s);
+    tile += stride;
   }
 }
 
@@ -352,7 +399,8 @@ Shape pick_shape(int n_rows, int K_pad, bool swiglu) {
 }
 
 template <int MODE>
-int launch(const GemvArgs &proto, bool swiglu, cudaStream_t st) {
+int launch(const GemvArgs &proto, cudaStream_t st) {
+  constexpr bool swiglu = MODE == 1;
   GemvArgs a = proto;
   const Shape sh = pick_shape(a.n_rows, a.K_pad, swiglu);
   if (sh.R == 0) return kDims;  // K beyond 16 slices of 2048 is not supported by this path
@@ -378,13 +426,13 @@ int launch(const GemvArgs &proto, bool swiglu, cudaStream_t st) {
 
   if (sh.C == 2) {
     if (sh.R == 2) {
-      if constexpr (MODE == 0) CHR_LAUNCH(2, 2); else return kLaunch;
+      if constexpr (MODE != 1) CHR_LAUNCH(2, 2); else return kLaunch;
     } else {
       CHR_LAUNCH(1, 2);
     }
   } else {
     if (sh.R == 4) {
-      if constexpr (MODE == 0) CHR_LAUNCH(4, 1); else return kLaunch;
+      if constexpr (MODE != 1) CHR_LAUNCH(4, 1); else return kLaunch;
     } else if (sh.R == 2) {
       CHR_LAUNCH(2, 1);
     } else {
@@ -418,7 +466,7 @@ extern "C" int chr_nf4_gemv(const chr_nf4_dev_t *w, const void *x, void *y, void
   a.x = static_cast<const __nv_bfloat16 *>(x);
   a.rms_w = static_cast<const __nv_bfloat16 *>(rms_w);
   a.rms_eps = rms_eps;
-  return launch<0>(a, false, static_cast<cudaStream_t>(stream));
+  return launch<0>(a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int chr_nf4_gemv_qkv(const chr_nf4_dev_t *q, const chr_nf4_dev_t *k,
@@ -459,7 +507,7 @@ extern "C" int chr_nf4_gemv_qkv(const chr_nf4_dev_t *q, const chr_nf4_dev_t *k,
   a.x = static_cast<const __nv_bfloat16 *>(x);
   a.rms_w = static_cast<const __nv_bfloat16 *>(rms_w);
   a.rms_eps = rms_eps;
-  return launch<0>(a, false, static_cast<cudaStream_t>(stream));
+  return launch<2>(a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int chr_nf4_gemv_swiglu(const chr_nf4_dev_t *gate, const chr_nf4_dev_t *up,
@@ -489,5 +537,5 @@ extern "C" int chr_nf4_gemv_swiglu(const chr_nf4_dev_t *gate, const chr_nf4_dev_
   a.x = static_cast<const __nv_bfloat16 *>(x);
   a.rms_w = static_cast<const __nv_bfloat16 *>(rms_w);
   a.rms_eps = rms_eps;
-  return launch<1>(a, true, static_cast<cudaStream_t>(stream));
+  return launch<1>(a, static_cast<cudaStream_t>(stream));
 }

@@ -82,19 +82,35 @@ __device__ __forceinline__ uint16_t ld_stream_u16(const void *p) {
   return v;
 }
 
-// Two FP32 fused multiply-adds in one instruction (sm_100 packed FP32).
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-  unsigned long long ra = *reinterpret_cast<unsigned long long *>(&a);
-  unsigned long long rb = *reinterpret_cast<unsigned long long *>(&b);
-  unsigned long long rc = *reinterpret_cast<unsigned long long *>(&c);
-  unsigned long long rd;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
-  return *reinterpret_cast<float2 *>(&rd);
+// Packed FP32 pairs live in 64-bit registers end to end, so that no pack/unpack
+// moves surround the packed FMA (fma.rn.f32x2, sm_100).
+typedef unsigned long long f32x2_t;
+
+__device__ __forceinline__ f32x2_t pack_f32x2(float lo, float hi) {
+  f32x2_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
 }
 
-__device__ __forceinline__ float2 lds_f2(uint32_t saddr) {
-  float2 v;
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(saddr));
+__device__ __forceinline__ void unpack_f32x2(f32x2_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__device__ __forceinline__ f32x2_t ffma2(f32x2_t a, f32x2_t b, f32x2_t c) {
+  f32x2_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+__device__ __forceinline__ f32x2_t fmul2(f32x2_t a, f32x2_t b) {
+  f32x2_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+__device__ __forceinline__ f32x2_t lds_f32x2(uint32_t saddr) {
+  f32x2_t v;
+  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(saddr));
   return v;
 }
 
@@ -108,6 +124,33 @@ __device__ __forceinline__ float warp_max_xor(float v) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
   return v;
+}
+
+// sum(x^2) over n bf16 values computed by ONE warp in a fixed order (lane l owns
+// the 8-element groups l, l+32, ...; xor butterfly), so every warp of every
+// kernel that needs the RMSNorm scale gets the same bits.
+__device__ __forceinline__ float warp_sumsq_bf16(const __nv_bfloat16 *__restrict__ x, int n,
+                                                int lane) {
+  float acc = 0.f;
+  const int n8 = n >> 3;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+#pragma unroll 4
+  for (int g = lane; g < n8; g += 32) {
+    const uint4 v = __ldg(xv + g);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float lo = bf16_lo(w[e]);
+      const float hi = bf16_hi(w[e]);
+      acc = fmaf(lo, lo, acc);
+      acc = fmaf(hi, hi, acc);
+    }
+  }
+  for (int i = (n8 << 3) + lane; i < n; i += 32) {
+    const float v = __bfloat162float(x[i]);
+    acc = fmaf(v, v, acc);
+  }
+  return warp_sum_xor(acc);
 }
 
 }  // namespace chr

@@ -73,8 +73,9 @@ class GraphSafeKV:
         self.v[layer, start:end].copy_(v.reshape(n, self.n_kv, self.head_dim))
 
     def mark_written(self, position: torch.Tensor) -> None:
-        """``valid_len = position + 1`` in tensor math (capturable)."""
-        self.valid_len.copy_((position.reshape(()).to(dtype=torch.int32) + 1).to(torch.int32))
+        """``valid_len = position + 1`` in place (capturable, no temporaries)."""
+        self.valid_len.copy_(position.reshape(()))
+        self.valid_len.add_(1)
 
 
 @dataclass

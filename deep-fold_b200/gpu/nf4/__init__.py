@@ -28,6 +28,7 @@ __all__ = [
     "nf4_attn",
     "nf4_embed_rows",
     "nf4_gemm",
+    "nf4_gemm_status",
     "nf4_gemv",
     "nf4_pick_commit",
     "nf4_plan",
@@ -185,6 +186,11 @@ def nf4_set_tuning(path: int = 0, split_k: int = 0, one_wave: int = 0) -> None:
     """Planner override for one process: ``path`` 0 auto / 1 tensor-core / 2 SIMT,
     ``split_k`` 0 auto or forced, ``one_wave`` 0 = this GPU's SM count."""
     _lib.load().chr_nf4_set_tuning(int(path), int(split_k), int(one_wave))
+
+
+def nf4_gemm_status() -> int:
+    """Read and clear the tensor-core GEMM's status word (0 = healthy). Synchronises."""
+    return int(_lib.load().chr_nf4_gemm_status())
 
 
 def nf4_version() -> str:

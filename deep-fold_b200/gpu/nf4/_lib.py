@@ -7,11 +7,13 @@ import of any op fails loudly. Build it with ``python deep-fold_b200/csrc/build.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 from pathlib import Path
 
 _DIR = Path(__file__).resolve().parent
-LIB_PATH = _DIR / "libchr_nf4.so"
+#: ``CHR_NF4_LIB`` points at another build of the same C ABI (A/B of kernel variants).
+LIB_PATH = Path(os.environ.get("CHR_NF4_LIB") or _DIR / "libchr_nf4.so")
 
 
 class ChrNf4Dev(Structure):
@@ -78,6 +80,7 @@ SIGNATURES = {
     ),
     "chr_nf4_rms": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_float, c_void_p]),
     "chr_nf4_version": (c_char_p, []),
+    "chr_nf4_gemm_status": (c_int, []),
     "chr_nf4_embed_rows": (
         c_int, [_DEV, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     ),

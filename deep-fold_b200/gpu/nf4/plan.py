@@ -61,13 +61,14 @@ def tc_tile(n: int) -> tuple[int, int, int, int]:
     """(bm, bk, block, dynamic shared bytes) of the tensor-core kernel for N."""
     bn = tc_bn(n)
     stages = 4
-    per_stage = 128 * 32 + 128 * 64 * 2 + 64 * bn * 2  # packed + bf16 A + bf16 B
-    return 128, 64, 192, stages * per_stage + 1024 + 1024
+    per_stage = 128 * 32 + 128 * 64 * 2 + bn * 64 * 2  # packed codes + bf16 A + bf16 B
+    return 128, 64, 192, stages * per_stage + 1024 + 256
 
 
 def tc_supported(m: int, kp: int, n: int) -> bool:
-    """Shapes the tensor-core kernel takes; everything else runs the SIMT tile."""
-    return False
+    """Shapes the tensor-core kernel takes: the packed row pitch must be a multiple
+    of 16 bytes (always true for K_pad a multiple of 64) and N <= 64."""
+    return 1 <= int(n) <= PLAN_MAX_N and (int(kp) // 2) % 16 == 0
 
 
 @dataclass(frozen=True)

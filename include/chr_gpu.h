@@ -132,6 +132,12 @@ int chr_nf4_rms(const void *x, const void *w, void *y, int32_t n, float eps,
 /* Library identification: "chr_nf4 sm_100a <build tag>". */
 const char *chr_nf4_version(void);
 
+/* Reads and clears the tensor-core GEMM's device status word (synchronises the
+ * device): 0 = every bounded pipeline wait completed; 1..4 = the TMA producer /
+ * MMA issuer / dequant warps / epilogue gave up on a wait and the affected
+ * launch's output is undefined. */
+int chr_nf4_gemm_status(void);
+
 /* Rows ids[0..n) of an NF4 table decoded to bf16( f32(LUT)*f32(scale) ),
  * out bf16 [n, K]. ids: device int64. An id outside [0, M) yields a zero row
  * and sets *status (device int32, optional) to 1. When position and valid_len

@@ -91,7 +91,8 @@ def test_graph_replay_equals_eager(spec, seed):
     for _ in range(8):
         graph.replay()
         out.append(int(s_graph.token.item()))
-    assert out == eager
+    # the eager helper stops at EOS, the replay loop does not
+    assert out[: len(eager)] == eager and (len(eager) == 9 or eager[-1] == spec.eos_id)
     assert int(s_graph.position.item()) == len(prompt) + 8
     assert int(s_graph.valid_len.item()) == len(prompt) + 8
 
@@ -104,9 +105,11 @@ def test_step_path_does_not_allocate():
     greedy_decode(state, weights)
     torch.cuda.synchronize()
     before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    held = torch.cuda.memory_allocated()
     for _ in range(4):
         greedy_decode(state, weights)
     torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == held
     assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
 
 
