@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(kRmsThreads) rms_kernel(const __nv_bfloat16 *_
                                                          __nv_bfloat16 *__restrict__ y, int n,
                                                          float eps) {
   const int tid = threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
   // same warp-level sum as the GEMV kernels' fused RMSNorm: identical scale bits
   const float s = rsqrtf(warp_sumsq_bf16(x, n, tid & 31) / static_cast<float>(n) + eps);
   for (int i = tid; i < n; i += kRmsThreads) {
@@ -39,6 +41,8 @@ __global__ void rope_kv_kernel(__nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__r
                                const __nv_bfloat16 *__restrict__ sin,
                                const int64_t *__restrict__ position, int n_q, int n_kv, int hd,
                                int max_seq) {
+  pdl_trigger();
+  pdl_wait();
   const long long pos = *position;
   if (pos < 0 || pos >= max_seq) return;
   const int head = blockIdx.x;
@@ -68,7 +72,8 @@ __global__ void rope_kv_kernel(__nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__r
 // ----------------------------------------------------------------------------
 // GQA decode attention  (reference: gpu/nf4/nf4_gemv.cu:558-727)
 // ----------------------------------------------------------------------------
-constexpr int kAttnWarps = 4;
+constexpr int kAttnWarps = 8;
+constexpr int kAttnMaxSplit = 16;  // splits actually used: min(n_split, 16)
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr float kNegInit = -1.0e30f;
 
@@ -108,6 +113,8 @@ attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_ca
   const int warp = tid >> 5;
   const int half = hd >> 1;
 
+  pdl_trigger();
+  pdl_wait();  // q, k_act, v_act, position and valid_len come from earlier kernels
   int vl = *valid_len;
   vl = vl < 0 ? 0 : (vl > max_seq ? max_seq : vl);
 
@@ -300,23 +307,31 @@ attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_ca
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // softmax weights of the splits, once per head: w[h][s] = exp(m_s - max) / sum
+  float *wts = &sm_o[0][0][0];  // the combine buffer is free again
+  for (int h = warp; h < nh; h += kAttnWarps) {
+    const size_t base = static_cast<size_t>(h_first + h) * n_split;
+    const float ms = lane < n_split ? __ldcg(m_s + base + lane) : kNegInit;
+    const float ls = lane < n_split ? __ldcg(l_s + base + lane) : 0.f;
+    const float mm = warp_max_xor(ms);
+    const float a = __expf(ms - mm);
+    const float ll = warp_sum_xor(a * ls);
+    if (lane < kAttnMaxSplit) wts[h * kAttnMaxSplit + lane] = ll > 0.f ? a / ll : 0.f;
+  }
+  __syncthreads();
   for (int i = tid; i < nh * hd; i += kAttnThreads) {
     const int h = i / hd;
     const int d = i - h * hd;
-    const size_t base = static_cast<size_t>(h_first + h) * n_split;
-    const volatile float *mh = m_s + base;
-    const volatile float *lh = l_s + base;
-    const volatile float *oh = o_s + base * hd + d;
-    float mm = kNegInit;
-    for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, mh[s]);
-    float ll = 0.f, oo = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < n_split; ++s) {
-      const float a = __expf(mh[s] - mm);
-      ll += a * lh[s];
-      oo += a * oh[static_cast<size_t>(s) * hd];
+    const float *oh = o_s + static_cast<size_t>(h_first + h) * n_split * hd + d;
+    float v[kAttnMaxSplit];
+#pragma unroll
+    for (int sidx = 0; sidx < kAttnMaxSplit; ++sidx) {
+      v[sidx] = sidx < n_split ? __ldcg(oh + static_cast<size_t>(sidx) * hd) : 0.f;
     }
-    out[static_cast<size_t>(h_first + h) * hd + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+    float oo = 0.f;
+#pragma unroll
+    for (int sidx = 0; sidx < kAttnMaxSplit; ++sidx) oo += wts[h * kAttnMaxSplit + sidx] * v[sidx];
+    out[static_cast<size_t>(h_first + h) * hd + d] = __float2bfloat16(oo);
   }
 }
 
@@ -328,6 +343,8 @@ __global__ void embed_rows_kernel(const uint8_t *__restrict__ packed,
                                   const int64_t *__restrict__ ids, __nv_bfloat16 *__restrict__ out,
                                   int32_t *status, const int64_t *position, int32_t *valid_len,
                                   int M, int K, int K_pad) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.y;
   if (r == 0 && blockIdx.x == 0 && threadIdx.x == 0 && position != nullptr &&
       valid_len != nullptr) {
@@ -387,6 +404,8 @@ pick_commit_kernel(const __nv_bfloat16 *__restrict__ logits, int n, int64_t *nex
                    unsigned long long *best, unsigned int *ticket) {
   __shared__ unsigned long long red[kPickThreads / 32];
   __shared__ bool last;
+  pdl_trigger();
+  pdl_wait();
   unsigned long long key = 0ull;
   const int stride = gridDim.x * kPickThreads;
   for (int i = blockIdx.x * kPickThreads + threadIdx.x; i < n; i += stride) {
@@ -429,10 +448,11 @@ extern "C" int chr_nf4_rms(const void *x, const void *w, void *y, int32_t n, flo
                            void *stream) {
   if (x == nullptr || w == nullptr || y == nullptr) return kNull;
   if (n < 1) return kDims;
-  rms_kernel<<<1, kRmsThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  const cudaError_t e = launch_chain(
+      rms_kernel, dim3(1), dim3(kRmsThreads), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(w),
       static_cast<__nv_bfloat16 *>(y), n, eps);
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+  return e == cudaSuccess ? kOk : kLaunch;
 }
 
 extern "C" int chr_nf4_rope_kv(void *q, void *k, const void *v, void *k_cache, void *v_cache,
@@ -444,13 +464,14 @@ extern "C" int chr_nf4_rope_kv(void *q, void *k, const void *v, void *k_cache, v
     return kNull;
   }
   if (n_q < 1 || n_kv < 1 || hd < 2 || (hd & 1) != 0 || max_seq < 1) return kDims;
-  rope_kv_kernel<<<static_cast<unsigned>(n_q + n_kv), 64, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16 *>(q), static_cast<__nv_bfloat16 *>(k),
-      static_cast<const __nv_bfloat16 *>(v), static_cast<__nv_bfloat16 *>(k_cache),
-      static_cast<__nv_bfloat16 *>(v_cache), static_cast<const __nv_bfloat16 *>(cos),
-      static_cast<const __nv_bfloat16 *>(sin), static_cast<const int64_t *>(position), n_q, n_kv,
-      hd, max_seq);
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+  const cudaError_t e = launch_chain(
+      rope_kv_kernel, dim3(static_cast<unsigned>(n_q + n_kv)), dim3(64), 0,
+      static_cast<cudaStream_t>(stream), static_cast<__nv_bfloat16 *>(q),
+      static_cast<__nv_bfloat16 *>(k), static_cast<const __nv_bfloat16 *>(v),
+      static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache),
+      static_cast<const __nv_bfloat16 *>(cos), static_cast<const __nv_bfloat16 *>(sin),
+      static_cast<const int64_t *>(position), n_q, n_kv, hd, max_seq);
+  return e == cudaSuccess ? kOk : kLaunch;
 }
 
 extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *out,
@@ -467,6 +488,10 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
     return kDims;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The workspace is sized for the caller's n_split; at most 16 splits are used
+  // (8 warps per CTA keep the same number of rows in flight), which halves the
+  // partials the merging CTA has to read back.
+  if (n_split > kAttnMaxSplit) n_split = kAttnMaxSplit;
   const int slots = n_q * n_split;
   float *m_s = ws;
   float *l_s = ws + slots;
@@ -483,23 +508,24 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
   auto *pp = static_cast<const int64_t *>(position);
 
 #define CHR_ATTN(PP, HH)                                                                       \
-  attn_split_kernel<PP, HH>                                                                    \
-      <<<dim3(static_cast<unsigned>(n_split), static_cast<unsigned>(n_kv),                     \
-              static_cast<unsigned>((n_rep + HH - 1) / HH)),                                   \
-         kAttnThreads, 0, st>>>(qp, kp, vp, static_cast<__nv_bfloat16 *>(out), m_s, l_s, o_s,  \
-                                vl, ka, va, cp, sp, pp, n_q, n_kv, hd, n_split, max_seq, scale)
+  launch_chain(attn_split_kernel<PP, HH>,                                                      \
+               dim3(static_cast<unsigned>(n_split), static_cast<unsigned>(n_kv),               \
+                    static_cast<unsigned>((n_rep + HH - 1) / HH)),                             \
+               dim3(kAttnThreads), 0, st, qp, kp, vp, static_cast<__nv_bfloat16 *>(out), m_s,  \
+               l_s, o_s, vl, ka, va, cp, sp, pp, n_q, n_kv, hd, n_split, max_seq, scale)
+  cudaError_t e;
   if (hd <= 64) {
     if (n_kv * ((n_rep + 7) / 8) > kMaxAttnGroups) return kDims;
-    CHR_ATTN(1, 8);
+    e = CHR_ATTN(1, 8);
   } else if (hd <= 128) {
     if (n_kv * ((n_rep + 7) / 8) > kMaxAttnGroups) return kDims;
-    CHR_ATTN(2, 8);
+    e = CHR_ATTN(2, 8);
   } else {
     if (n_kv * ((n_rep + 3) / 4) > kMaxAttnGroups) return kDims;
-    CHR_ATTN(4, 4);
+    e = CHR_ATTN(4, 4);
   }
 #undef CHR_ATTN
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+  return e == cudaSuccess ? kOk : kLaunch;
 }
 
 extern "C" int chr_nf4_embed_rows(const chr_nf4_dev_t *w, const void *ids, int32_t n, void *out,
@@ -513,11 +539,12 @@ extern "C" int chr_nf4_embed_rows(const chr_nf4_dev_t *w, const void *ids, int32
   const int c8 = (w->K + 7) / 8;
   const int threads = 128;
   const dim3 grid(static_cast<unsigned>((c8 + threads - 1) / threads), static_cast<unsigned>(n));
-  embed_rows_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      w->packed, w->scale, static_cast<const int64_t *>(ids), static_cast<__nv_bfloat16 *>(out),
+  const cudaError_t e = launch_chain(
+      embed_rows_kernel, grid, dim3(threads), 0, static_cast<cudaStream_t>(stream), w->packed,
+      w->scale, static_cast<const int64_t *>(ids), static_cast<__nv_bfloat16 *>(out),
       static_cast<int32_t *>(status), static_cast<const int64_t *>(position),
       static_cast<int32_t *>(valid_len), w->M, w->K, w->K_pad);
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+  return e == cudaSuccess ? kOk : kLaunch;
 }
 
 extern "C" int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_token, void *token,
@@ -531,10 +558,10 @@ extern "C" int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_tok
   blocks = blocks < 1 ? 1 : (blocks > sms ? sms : blocks);
   auto *best = static_cast<unsigned long long *>(scratch);
   auto *ticket = reinterpret_cast<unsigned int *>(best + 1);
-  pick_commit_kernel<<<static_cast<unsigned>(blocks), kPickThreads, 0,
-                       static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16 *>(logits), n, static_cast<int64_t *>(next_token),
-      static_cast<int64_t *>(token), static_cast<int64_t *>(position),
-      static_cast<uint8_t *>(finished), eos, best, ticket);
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+  const cudaError_t e = launch_chain(
+      pick_commit_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kPickThreads), 0,
+      static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16 *>(logits), n,
+      static_cast<int64_t *>(next_token), static_cast<int64_t *>(token),
+      static_cast<int64_t *>(position), static_cast<uint8_t *>(finished), eos, best, ticket);
+  return e == cudaSuccess ? kOk : kLaunch;
 }

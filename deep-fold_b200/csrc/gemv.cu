@@ -220,8 +220,10 @@ nf4_gemv_kernel(const GemvArgs a) {
     }
   };
 
-  // The first tile's weights depend on nothing this kernel computes: put them in
-  // flight before the table is built and x is read.
+  // The first tile's weights depend on nothing the previous kernel writes: put them
+  // in flight, and let the next kernel of the chain start launching, before the
+  // table is built and x is read.
+  pdl_trigger();
   int tile = blockIdx.x;
   issue(tile, cur, cur_s);
 
@@ -237,6 +239,9 @@ nf4_gemv_kernel(const GemvArgs a) {
     asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(lo), "f"(hi));
   }
   const uint32_t tab_lane = tab_base + static_cast<uint32_t>(lane) * 8u;
+
+  // x (and the residual / outputs) belong to the previous kernel until it completes.
+  pdl_wait();
 
   // Optional fused RMSNorm: every warp derives the same scale on its own.
   float inv = 1.f;
@@ -421,7 +426,10 @@ int launch(const GemvArgs &proto, cudaStream_t st) {
       }                                                                                      \
       attr_done = true;                                                                      \
     }                                                                                        \
-    nf4_gemv_kernel<RR, CC, MODE><<<grid, block, kSmemBytes, st>>>(a);                       \
+    if (launch_chain(nf4_gemv_kernel<RR, CC, MODE>, grid, block, kSmemBytes, st, a) !=       \
+        cudaSuccess) {                                                                       \
+      return kLaunch;                                                                        \
+    }                                                                                        \
   } while (0)
 
   if (sh.C == 2) {

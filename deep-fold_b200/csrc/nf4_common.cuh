@@ -48,6 +48,34 @@ inline int check_matrix(const chr_nf4_dev_t *w) {
   return kOk;
 }
 
+// Programmatic dependent launch: kernels of the decode chain are launched with the
+// programmatic-stream-serialization attribute, so a kernel's CTAs may start (and
+// prefetch weights, build tables) while the previous kernel drains; pdl_wait()
+// orders everything after it behind the previous kernel's completion. Both
+// instructions are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+bool pdl_enabled();
+void set_pdl_enabled(bool on);
+
+// Launch with or without the programmatic attribute (process-wide switch).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline int sm_count() {
   static int cached = 0;
   if (cached > 0) return cached;

@@ -5,3 +5,23 @@
 #endif
 
 extern "C" const char *chr_nf4_version(void) { return "chr_nf4 sm_100a " CHR_BUILD_TAG; }
+
+#include <cstdlib>
+
+#include "nf4_common.cuh"
+
+namespace chr {
+namespace {
+bool &pdl_flag() {
+  static bool on = [] {
+    const char *v = std::getenv("CHR_NF4_PDL");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
+}  // namespace
+bool pdl_enabled() { return pdl_flag(); }
+void set_pdl_enabled(bool on) { pdl_flag() = on; }
+}  // namespace chr
+
+extern "C" void chr_nf4_set_pdl(int32_t on) { chr::set_pdl_enabled(on != 0); }

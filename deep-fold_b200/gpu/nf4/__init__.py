@@ -35,6 +35,7 @@ __all__ = [
     "nf4_qkv",
     "nf4_rms",
     "nf4_rope_kv",
+    "nf4_set_pdl",
     "nf4_set_tuning",
     "nf4_swiglu",
     "nf4_version",
@@ -186,6 +187,11 @@ def nf4_set_tuning(path: int = 0, split_k: int = 0, one_wave: int = 0) -> None:
     """Planner override for one process: ``path`` 0 auto / 1 tensor-core / 2 SIMT,
     ``split_k`` 0 auto or forced, ``one_wave`` 0 = this GPU's SM count."""
     _lib.load().chr_nf4_set_tuning(int(path), int(split_k), int(one_wave))
+
+
+def nf4_set_pdl(on: bool = True) -> None:
+    """Programmatic dependent launch for the decode-chain kernels (default on)."""
+    _lib.load().chr_nf4_set_pdl(1 if on else 0)
 
 
 def nf4_gemm_status() -> int:

@@ -132,6 +132,12 @@ int chr_nf4_rms(const void *x, const void *w, void *y, int32_t n, float eps,
 /* Library identification: "chr_nf4 sm_100a <build tag>". */
 const char *chr_nf4_version(void);
 
+/* Programmatic dependent launch for the decode-chain kernels (GEMV family,
+ * attention, embedding rows, pick): on (default, or CHR_NF4_PDL=1) lets a kernel's
+ * prologue overlap the previous kernel's tail, inside CUDA graphs as well; 0
+ * restores plain stream order. Results are identical either way. */
+void chr_nf4_set_pdl(int32_t on);
+
 /* Reads and clears the tensor-core GEMM's device status word (synchronises the
  * device): 0 = every bounded pipeline wait completed; 1..4 = the TMA producer /
  * MMA issuer / dequant warps / epilogue gave up on a wait and the affected
