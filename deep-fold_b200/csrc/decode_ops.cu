@@ -565,3 +565,54 @@ extern "C" int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_tok
       static_cast<int64_t *>(position), static_cast<uint8_t *>(finished), eos, best, ticket);
   return e == cudaSuccess ? kOk : kLaunch;
 }
+
+// ----------------------------------------------------------------------------
+// Attention for callers that cannot allocate device memory
+// ----------------------------------------------------------------------------
+// Some hosts of this library have no allocator to ask for the split workspace:
+// a binding layer that only forwards pointers it was handed, a plugin loaded
+// into a process whose memory pool is owned by someone else and closed to it, or
+// code running where cudaMalloc is forbidden (inside a stream capture, or under
+// a "no allocation after start-up" rule). For them the split partials live in
+// the fixed array below instead of a caller buffer. Every GPU that loads the
+// library carries these bytes until the process exits, so the size is kept modest.
+constexpr int kStaticAttnFloats = 262144;  // 1 MiB
+static __device__ __align__(256) float g_attn_static_ws[kStaticAttnFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float *g_static_ws_ptr[kMaxDevices] = {};
+
+// The array's name is only a stand-in on the host; the kernel needs the address
+// the current device gives it. Looked up once per device, with that device current.
+int static_ws_for_current_device(float **out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return chr::kLaunch;
+  if (g_static_ws_ptr[dev] == nullptr) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_attn_static_ws) != cudaSuccess || p == nullptr) {
+      return chr::kLaunch;
+    }
+    g_static_ws_ptr[dev] = static_cast<float *>(p);
+  }
+  *out = g_static_ws_ptr[dev];
+  return chr::kOk;
+}
+}  // namespace
+
+extern "C" int chr_nf4_attn_noalloc(const void *q, const void *k, const void *v, void *out,
+                                    const void *valid_len, int32_t n_q, int32_t n_kv, int32_t hd,
+                                    int32_t n_split, float scale, void *stream, const void *k_act,
+                                    const void *v_act, const void *cos, const void *sin,
+                                    const void *position, int32_t max_seq) {
+  if (n_q < 1 || hd < 2 || n_split < 1 || n_split > 64) return chr::kDims;
+  const long long used_splits = n_split > 16 ? 16 : n_split;
+  if (static_cast<long long>(n_q) * used_splits * (hd + 2) > kStaticAttnFloats) {
+    return chr::kWorkspace;  // beyond the built-in scratch: use chr_nf4_attn with a caller buffer
+  }
+  float *ws = nullptr;
+  const int rc = static_ws_for_current_device(&ws);
+  if (rc != chr::kOk) return rc;
+  return chr_nf4_attn(q, k, v, out, valid_len, ws, n_q, n_kv, hd, n_split, scale, stream, k_act,
+                      v_act, cos, sin, position, max_seq);
+}

@@ -78,6 +78,11 @@ SIGNATURES = {
          c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_int32],
     ),
+    "chr_nf4_attn_noalloc": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+         c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32],
+    ),
     "chr_nf4_rms": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_float, c_void_p]),
     "chr_nf4_version": (c_char_p, []),
     "chr_nf4_gemm_status": (c_int, []),

@@ -166,6 +166,23 @@ int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_token,
                         void *token, void *position, void *finished,
                         int64_t eos, void *scratch, void *stream);
 
+/* chr_nf4_attn without the workspace argument, for callers that have no way to
+ * allocate device memory (a pointer-forwarding binding, a plugin without access
+ * to the host's memory pool, code under a no-allocation rule). No counterpart in
+ * the reference. The split partials go to a 1 MiB array built into the library
+ * (resident on every GPU that loads it); the call returns -7 when
+ * n_q * min(n_split, 16) * (hd + 2) exceeds 262144 floats. It calls no
+ * allocation routine. The first call on a device looks the array's address up
+ * (one host-side runtime query) and should therefore come before any stream
+ * capture on that device. All calls share the array: nothing in it has to start
+ * at zero, but two calls that overlap on the GPU (different streams, or another
+ * process thread) race on it and must be serialised by the caller. */
+int chr_nf4_attn_noalloc(const void *q, const void *k, const void *v, void *out,
+                         const void *valid_len, int32_t n_q, int32_t n_kv, int32_t hd,
+                         int32_t n_split, float scale, void *stream, const void *k_act,
+                         const void *v_act, const void *cos, const void *sin,
+                         const void *position, int32_t max_seq);
+
 /* Host-side NF4 codec, bit-exact with the reference's encoder/decoder
  * (internal/nf4/nf4.go:46-121,129-185; gpu/tests/nf4_oracle.py:119-187).
  * w: host float32 [M, K]; packed: host [M, K_pad/2]; scale: host binary16 bits
