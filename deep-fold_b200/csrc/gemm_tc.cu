@@ -402,6 +402,301 @@ int launch(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y, int
 
 int bn_for(int N) { return N <= 16 ? 16 : (N <= 32 ? 32 : 64); }
 
+// =============================================================================
+// Wide GEMM on activation rows: y_rows[N, M] = x_rows[N, K] . dequant(W)^T
+// =============================================================================
+// Same pipeline, three differences: the activation tile is already K-major in
+// global memory (row n of x_rows holds K contiguous values), so TMA loads it
+// straight into the 128-byte-swizzled B tile; eight warps dequantize (two threads
+// per W row, 32 codes each), which keeps the codebook work ahead of the tensor core
+// at BN up to 256; the epilogue writes the transposed tile (consecutive lanes own
+// consecutive m, so every store instruction covers 64 contiguous bytes).
+constexpr int rThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 dequant + epilogue
+constexpr int rDequant = 256;
+
+__host__ __device__ constexpr int rows_stage_bytes(int bn) { return tRawBytes + tABytes + bn * tBK * 2; }
+__host__ __device__ constexpr int rows_stages(int bn) { return bn > 128 ? 4 : 6; }
+__host__ __device__ constexpr int rows_smem_bytes(int bn) {
+  return rows_stages(bn) * rows_stage_bytes(bn) + 1024 + 256;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(rThreads, 1)
+gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
+                 const __grid_constant__ CUtensorMap x_map, const uint16_t *__restrict__ scale,
+                 __nv_bfloat16 *__restrict__ y, float *__restrict__ partial, int M, int K,
+                 int K_pad, int N, int n_ktiles, int tiles_per_split) {
+  constexpr int kStages = rows_stages(BN);
+  constexpr int kBBytes = BN * tBK * 2;
+  constexpr uint32_t kCols = BN < 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float lut[16];
+  __shared__ uint32_t tmem_slot;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int m0 = blockIdx.x * tBM;
+  const int n0 = blockIdx.y * BN;
+  const int kt0 = blockIdx.z * tiles_per_split;
+  const int kt1 = min(n_ktiles, kt0 + tiles_per_split);
+  const int n_local = kt1 - kt0;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  auto a_tile = [&](int s) { return base + s * tABytes; };
+  auto b_tile = [&](int s) { return base + kStages * tABytes + s * kBBytes; };
+  auto raw_tile = [&](int s) { return base + kStages * (tABytes + kBBytes) + s * tRawBytes; };
+  const uint32_t bars = base + kStages * rows_stage_bytes(BN);
+  auto in_full = [&](int s) { return bars + 8 * s; };                   // TMA: codes + x tile
+  auto ab_full = [&](int s) { return bars + 8 * (kStages + s); };       // dequant done
+  auto empty = [&](int s) { return bars + 8 * (2 * kStages + s); };     // MMA done with stage
+  const uint32_t acc_full = bars + 8 * (3 * kStages);
+
+  if (tid < 16) lut[tid] = __uint_as_float(kLutBits[tid]);
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(in_full(s), 1);
+      mbar_init(ab_full(s), rDequant);
+      mbar_init(empty(s), 1);
+    }
+    mbar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(kCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; i < n_local && ok; ++i) {
+        const int s = i % kStages;
+        if (i >= kStages) ok = mbar_wait(empty(s), ((i / kStages) - 1) & 1);
+        if (!ok) break;
+        mbar_expect_tx(in_full(s), tRawBytes + kBBytes);
+        tma_load_2d(raw_tile(s), &packed_map, in_full(s), (kt0 + i) * (tBK / 2), m0);
+        tma_load_2d(b_tile(s), &x_map, in_full(s), (kt0 + i) * tBK, n0);
+        issued = i + 1;
+      }
+      if (!ok) {
+        atomicExch(&g_gemm_status, 5);
+        for (int i = max(0, issued - kStages); i < issued; ++i) {
+          mbar_wait(in_full(i % kStages), (i / kStages) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                 (static_cast<uint32_t>(BN >> 3) << 17) |
+                                 (static_cast<uint32_t>(tBM >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < n_local && ok; ++i) {
+        const int s = i % kStages;
+        ok = mbar_wait(ab_full(s), (i / kStages) & 1);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int k4 = 0; k4 < tBK / 16; ++k4) {
+          umma_bf16(tmem_d, umma_desc(a_tile(s) + k4 * 32), umma_desc(b_tile(s) + k4 * 32), idesc,
+                    (i > 0 || k4 > 0) ? 1u : 0u);
+        }
+        umma_commit(empty(s));
+      }
+      if (ok) {
+        umma_commit(acc_full);
+      } else {
+        atomicExch(&g_gemm_status, 6);
+      }
+    }
+  } else {
+    // ---------------- dequant: thread (row r, half h) owns 32 codes ----------------
+    const int t = tid - 64;                 // 0..255
+    const int r = t & 127;
+    const int hlf = t >> 7;
+    const int grow = m0 + r;
+    const bool row_live = grow < M;
+    const int n_groups = K_pad / kGroup;
+    const uint32_t a_row_off = static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
+    const int sw = r & 7;
+    bool ok = true;
+    uint16_t s_bits = 0;
+    if (row_live && n_local > 0) s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt0);
+    for (int i = 0; i < n_local && ok; ++i) {
+      const int s = i % kStages;
+      const int kt = kt0 + i;
+      const float sc = row_live ? half_bits_to_float(s_bits) : 0.f;
+      if (row_live && i + 1 < n_local) {
+        s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt + 1);
+      }
+      if (i >= kStages) ok = mbar_wait(empty(s), ((i / kStages) - 1) & 1);
+      if (!ok) break;
+      ok = mbar_wait(in_full(s), (i / kStages) & 1);
+      if (!ok) break;
+      uint4 pk;
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w)
+                   : "r"(raw_tile(s) + r * 32 + hlf * 16));
+      const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
+      const int k_base = kt * tBK + hlf * 32;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const int c = hlf * 4 + c4;
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t byte = (wv[c4] >> (8 * e)) & 0xFFu;
+          const int k = k_base + c4 * 8 + 2 * e;
+          float lo = lut[byte & 0xFu] * sc;
+          float hi = lut[byte >> 4] * sc;
+          if (k >= K) lo = 0.f;
+          if (k + 1 >= K) hi = 0.f;
+          o[e] = pack_bf16(lo, hi);
+        }
+        const uint32_t dst = a_tile(s) + a_row_off + static_cast<uint32_t>((c ^ sw) * 16);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o[0]), "r"(o[1]),
+                     "r"(o[2]), "r"(o[3])
+                     : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(ab_full(s));
+    }
+    if (!ok) atomicExch(&g_gemm_status, 7);
+
+    // ---------------- epilogue: two warps per TMEM lane quadrant ----------------
+    if (ok && n_local > 0) ok = mbar_wait(acc_full, 0);
+    if (!ok) atomicExch(&g_gemm_status, 8);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && n_local > 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int quad = warp & 3;
+      const int col_half = (warp - 2) >> 2;   // warps 2..5 -> 0, 6..9 -> 1
+      const int row = m0 + quad * 32 + lane;
+      constexpr int kHalf = BN / 2 >= 16 ? BN / 2 : 16;
+      const int c_begin = BN >= 32 ? col_half * kHalf : 0;
+      const int c_end = BN >= 32 ? c_begin + kHalf : (col_half == 0 ? BN : 0);
+      for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem_d + (static_cast<uint32_t>(quad * 32) << 16) + c0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < M) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int n = n0 + c0 + e;
+            if (n < N) {
+              const float f = __uint_as_float(v[e]);
+              if (partial != nullptr) {
+                partial[(static_cast<size_t>(blockIdx.z) * N + n) * M + row] = f;
+              } else {
+                y[static_cast<size_t>(n) * M + row] = __float2bfloat16(f);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kCols));
+  }
+}
+
+__global__ void reduce_rows_kernel(const float *__restrict__ partial, __nv_bfloat16 *__restrict__ y,
+                                   long long total, int splits) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float v = 0.f;
+  for (int s = 0; s < splits; ++s) v += partial[static_cast<size_t>(s) * total + i];
+  y[i] = __float2bfloat16(v);
+}
+
+struct RowsPlan {
+  int bn, grid_x, grid_y, split, tiles_per_split, n_ktiles;
+  long long ws_floats;
+};
+
+RowsPlan plan_rows(int M, int K_pad, int N, bool have_ws) {
+  RowsPlan p{};
+  const int n16 = ((N + 15) / 16) * 16;
+  p.bn = n16 <= 32 ? 32 : (n16 <= 64 ? 64 : (n16 <= 128 ? 128 : 256));
+  if (n16 <= 16) p.bn = 16;
+  p.grid_x = (M + tBM - 1) / tBM;
+  p.grid_y = (N + p.bn - 1) / p.bn;
+  p.n_ktiles = (K_pad + tBK - 1) / tBK;
+  int want = 1;
+  if (have_ws) {
+    const int ctas = p.grid_x * p.grid_y;
+    want = (sm_count() + ctas - 1) / ctas;          // one full wave
+    const int cap = p.n_ktiles / 4 > 0 ? p.n_ktiles / 4 : 1;  // at least four K tiles per split
+    if (want > cap) want = cap;
+  }
+  if (want < 1) want = 1;
+  p.tiles_per_split = (p.n_ktiles + want - 1) / want;
+  p.split = (p.n_ktiles + p.tiles_per_split - 1) / p.tiles_per_split;
+  p.ws_floats = p.split > 1 ? static_cast<long long>(p.split) * M * N : 0;
+  return p;
+}
+
+template <int BN>
+int launch_rows(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y, int N,
+                float *partial, const RowsPlan &p, cudaStream_t st) {
+  EncodeTiled enc = encode_fn();
+  if (enc == nullptr) return kLaunch;
+  CUtensorMap wmap, xmap;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(w.K_pad / 2), static_cast<cuuint64_t>(w.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(w.K_pad / 2)};
+    const cuuint32_t box[2] = {tBK / 2, tBM};
+    const cuuint32_t elem[2] = {1, 1};
+    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w.packed), dims, strides,
+            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      return kLaunch;
+    }
+  }
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(w.K), static_cast<cuuint64_t>(N)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(w.K) * 2};
+    const cuuint32_t box[2] = {tBK, static_cast<cuuint32_t>(BN)};
+    const cuuint32_t elem[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16 *>(x), dims,
+            strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      return kLaunch;
+    }
+  }
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(gemm_rows_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             rows_smem_bytes(BN)) != cudaSuccess) {
+      return kLaunch;
+    }
+    attr_done = true;
+  }
+  const dim3 grid(static_cast<unsigned>(p.grid_x), static_cast<unsigned>(p.grid_y),
+                  static_cast<unsigned>(p.split));
+  gemm_rows_kernel<BN><<<grid, rThreads, rows_smem_bytes(BN), st>>>(
+      wmap, xmap, w.scale, y, partial, w.M, w.K, w.K_pad, N, p.n_ktiles, p.tiles_per_split);
+  if (partial != nullptr) {
+    const long long total = static_cast<long long>(w.M) * N;
+    reduce_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(partial, y, total,
+                                                                                   p.split);
+  }
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+}
+
+
 }  // namespace
 
 TileShape tc_tile_shape(int N) {
@@ -435,4 +730,37 @@ extern "C" int chr_nf4_gemm_status(void) {
     cudaMemcpyToSymbol(chr::g_gemm_status, &zero, sizeof(int));
   }
   return v;
+}
+
+// Workspace (FP32 floats) chr_nf4_gemm_rows wants for this shape; 0 = none needed.
+extern "C" int64_t chr_nf4_gemm_rows_ws(const chr_nf4_dev_t *w, int32_t N) {
+  if (w == nullptr || N < 1 || w->M < 1 || w->K < 1 || !chr::k_pad_ok(w->K, w->K_pad)) return 0;
+  return chr::plan_rows(w->M, w->K_pad, N, true).ws_floats;
+}
+
+extern "C" int chr_nf4_gemm_rows(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows,
+                                 int32_t N, float *ws, int64_t ws_floats, void *stream) {
+  using namespace chr;
+  if (x_rows == nullptr || y_rows == nullptr) return kNull;
+  const int rc = check_matrix(w);
+  if (rc != kOk) return rc;
+  if (N < 1 || N > (1 << 20)) return kRangeN;
+  if ((w->K % 8) != 0) return kDims;  // the activation row pitch must be a multiple of 16 bytes
+  if (!aligned(w->packed, 16) || !aligned(x_rows, 16) || !aligned(w->scale, 2)) return kAlign;
+  RowsPlan p = plan_rows(w->M, w->K_pad, N, ws != nullptr && ws_floats > 0);
+  if (p.ws_floats > 0 && ws_floats < p.ws_floats) {
+    p = plan_rows(w->M, w->K_pad, N, false);
+    if (ws != nullptr && ws_floats > 0) return kWorkspace;
+  }
+  float *partial = p.split > 1 ? ws : nullptr;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto *xb = static_cast<const __nv_bfloat16 *>(x_rows);
+  auto *yb = static_cast<__nv_bfloat16 *>(y_rows);
+  switch (p.bn) {
+    case 16: return launch_rows<16>(*w, xb, yb, N, partial, p, st);
+    case 32: return launch_rows<32>(*w, xb, yb, N, partial, p, st);
+    case 64: return launch_rows<64>(*w, xb, yb, N, partial, p, st);
+    case 128: return launch_rows<128>(*w, xb, yb, N, partial, p, st);
+    default: return launch_rows<256>(*w, xb, yb, N, partial, p, st);
+  }
 }

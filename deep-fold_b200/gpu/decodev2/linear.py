@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from gpu.host.codec import encode_nf4, encode_nf4_device
-from gpu.nf4 import LIVE_MAX_N, nf4_gemm, nf4_gemv
+from gpu.nf4 import LIVE_MAX_N, nf4_gemm, nf4_gemm_rows, nf4_gemv
 from gpu.nf4.plan import k_pad
 
 from .arch import ArchSpec
@@ -28,9 +28,19 @@ __all__ = [
     "linear_backend",
     "nf4_linear",
     "set_linear_backend",
+    "set_rows_gemm",
 ]
 
 _BACKEND = "gemv"
+_ROWS_GEMM = True
+
+
+def set_rows_gemm(on: bool) -> None:
+    """``True`` (default): N > 1 linears take the wide row-layout GEMM in one call;
+    ``False``: the reference's shape, ``[K, N]`` chunks of ``LIVE_MAX_N`` through ``nf4_gemm``."""
+    global _ROWS_GEMM
+    _ROWS_GEMM = bool(on)
+
 
 
 def linear_backend() -> str:
@@ -109,6 +119,8 @@ def nf4_linear(mat: DeviceLinear, x: torch.Tensor) -> torch.Tensor:
         y = nf4_gemv(mat.packed, mat.scale, rows.reshape(mat.K), mat.M, mat.K, mat.K_pad).view(1, mat.M)
     elif n == 1:
         y = nf4_gemm(mat.packed, mat.scale, rows.reshape(mat.K), mat.M, mat.K, mat.K_pad).view(1, mat.M)
+    elif _ROWS_GEMM and mat.K % 8 == 0:
+        y = nf4_gemm_rows(mat.packed, mat.scale, rows.contiguous(), mat.M, mat.K, mat.K_pad)
     else:
         cols = []
         for lo in range(0, n, LIVE_MAX_N):

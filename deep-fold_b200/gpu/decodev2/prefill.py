@@ -21,8 +21,14 @@ from .state import DecodeState
 __all__ = ["forward_prefill", "prefill_chunk_width"]
 
 
+#: positions per prefill chunk when the caller does not say; the wide GEMM has no
+#: 32-column ceiling, so a chunk is bounded by attention-mask memory, not by the kernel.
+PREFILL_CHUNK = 512
+
+
 def prefill_chunk_width(state: DecodeState, chunk: int | None = None) -> int:
-    cap = min(int(LIVE_MAX_N), int(state.spec.max_seq))
+    """Positions per chunk. ``chunk=LIVE_MAX_N`` (32) reproduces the reference's chunking."""
+    cap = min(int(PREFILL_CHUNK), int(state.spec.max_seq))
     return cap if chunk is None else max(1, min(int(chunk), cap))
 
 

@@ -28,6 +28,7 @@ __all__ = [
     "nf4_attn",
     "nf4_embed_rows",
     "nf4_gemm",
+    "nf4_gemm_rows",
     "nf4_gemm_status",
     "nf4_gemv",
     "nf4_pick_commit",
@@ -164,6 +165,44 @@ def nf4_gemm(
     _lib.check(rc, "chr_nf4_gemm")
     del keep
     return y
+
+
+def nf4_gemm_rows(
+    packed: torch.Tensor,
+    scale: torch.Tensor,
+    x_rows: torch.Tensor,
+    M: int,  # noqa: N803
+    K: int,  # noqa: N803
+    K_pad: int,  # noqa: N803
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """``y[N, M] = x_rows[N, K] @ dequant(W).T`` on the tensor cores, any ``N >= 1``.
+
+    Activations keep their natural ``[tokens, features]`` layout on both sides.
+    Needs ``K % 8 == 0`` (TMA row pitch); other shapes go through :func:`nf4_gemm`.
+    """
+    if not x_rows.is_cuda or x_rows.dtype is not torch.bfloat16:
+        _fail("x_rows must be CUDA bfloat16")
+    if x_rows.dim() != 2 or x_rows.size(1) != int(K):
+        _fail("x_rows must be [N, K]")
+    if int(K) % 8:
+        _fail("nf4_gemm_rows needs K % 8 == 0")
+    dev, keep = _matrix(packed, scale, M, K, K_pad)
+    x_rows = x_rows.contiguous()
+    n = int(x_rows.size(0))
+    if n < 1:
+        _fail("x_rows must be non-empty")
+    if out is None:
+        out = torch.empty((n, int(M)), dtype=torch.bfloat16, device=x_rows.device)
+    else:
+        _out_vec(out, n * int(M))
+    lib = _lib.load()
+    need = int(lib.chr_nf4_gemm_rows_ws(ctypes.byref(dev), n))
+    ws = torch.empty(need, dtype=torch.float32, device=x_rows.device) if need > 0 else None
+    rc = lib.chr_nf4_gemm_rows(ctypes.byref(dev), _ptr(x_rows), _ptr(out), n, _ptr(ws), need, _stream())
+    _lib.check(rc, "chr_nf4_gemm_rows")
+    del keep
+    return out
 
 
 def nf4_plan(

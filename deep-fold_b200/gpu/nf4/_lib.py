@@ -87,6 +87,10 @@ SIGNATURES = {
     "chr_nf4_version": (c_char_p, []),
     "chr_nf4_gemm_status": (c_int, []),
     "chr_nf4_set_pdl": (None, [c_int32]),
+    "chr_nf4_gemm_rows_ws": (c_int64, [_DEV, c_int32]),
+    "chr_nf4_gemm_rows": (
+        c_int, [_DEV, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p]
+    ),
     "chr_nf4_embed_rows": (
         c_int, [_DEV, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     ),

@@ -132,6 +132,19 @@ int chr_nf4_rms(const void *x, const void *w, void *y, int32_t n, float eps,
 /* Library identification: "chr_nf4 sm_100a <build tag>". */
 const char *chr_nf4_version(void);
 
+/* Wide GEMM on activation rows: y_rows[N, M] = bf16( x_rows[N, K] . dequant(W)^T ),
+ * the layout activations already have ([tokens, features], K contiguous), so no
+ * transposes on either side and any N >= 1 in one call (tiled 16..256 columns per
+ * CTA). Same tcgen05 pipeline and numerics as chr_nf4_gemm; the activation tile is
+ * loaded by TMA, which needs K % 8 == 0 (-3 otherwise) and x_rows 16-byte aligned.
+ * ws: optional FP32 split-K workspace of chr_nf4_gemm_rows_ws(w, N) floats (0 = the
+ * shape fills the GPU without split-K); NULL pins split-K to 1; too small -> -7.
+ * Replaces the transpose + chunk loop around chr_nf4_gemm in
+ * gpu/decodev2/linear.py:101-136 and gpu/host/linear.py:31-81. */
+int64_t chr_nf4_gemm_rows_ws(const chr_nf4_dev_t *w, int32_t N);
+int chr_nf4_gemm_rows(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows, int32_t N,
+                      float *ws, int64_t ws_floats, void *stream);
+
 /* Programmatic dependent launch for the decode-chain kernels (GEMV family,
  * attention, embedding rows, pick): on (default, or CHR_NF4_PDL=1) lets a kernel's
  * prologue overlap the previous kernel's tail, inside CUDA graphs as well; 0

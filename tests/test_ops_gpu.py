@@ -349,6 +349,33 @@ def test_gemm_matches_oracle(m, k, n):
     assert torch.equal(y, nf4_gemm(pt, st, xt, m, k, o.padded_k(k), max_n=PLAN_MAX_N if n > 32 else 32))
 
 
+ROWS_CASES = [(128, 64, 16), (130, 72, 3), (2048, 2048, 512), (300, 1000, 33), (11008, 2048, 300),
+              (2048, 11008, 64), (4096, 4096, 1), (512, 512, 257)]
+
+
+@pytest.mark.parametrize("m,k,n", ROWS_CASES)
+def test_gemm_rows_matches_oracle(m, k, n):
+    from gpu.nf4 import nf4_gemm_rows, nf4_gemm_status
+
+    rng = np.random.default_rng(m + k + n)
+    p, s, pt, st = blobs(m, k, m * 3 + n, weight_like=(m * k > 100000))
+    xt, xf = bf16_vec(rng, n, k)
+    y = nf4_gemm_rows(pt, st, xt, m, k, o.padded_k(k))
+    assert y.shape == (n, m) and y.dtype is torch.bfloat16
+    want = xf.astype(np.float64) @ o.dequantize_bf16(p, s, m, k).astype(np.float64).T
+    assert_close(y, want.astype(np.float32), f"gemm_rows {m}x{k}x{n}")
+    assert torch.equal(y, nf4_gemm_rows(pt, st, xt, m, k, o.padded_k(k)))
+    assert nf4_gemm_status() == 0
+
+
+def test_gemm_rows_rejects_unaligned_k():
+    from gpu.nf4 import nf4_gemm_rows
+
+    _, _, pt, st = blobs(64, 65, 1, weight_like=False)
+    with pytest.raises(RuntimeError, match="K % 8"):
+        nf4_gemm_rows(pt, st, torch.zeros((4, 65), dtype=torch.bfloat16, device=DEV), 64, 65, 128)
+
+
 def test_gemm_no_column_leak_and_pad_garbage():
     from gpu.nf4 import nf4_gemm
 
