@@ -42,6 +42,7 @@ struct GemvArgs {
   const uint8_t *packed[3];
   const uint16_t *scale[3];
   __nv_bfloat16 *y[3];
+  float *y32;                     // MODE 0 only: when set, the FP32 sum is stored unrounded
   const __nv_bfloat16 *extra[3];  // residual (plain) or bias (fused q/k/v); may be null
   int rows_end[3];                // prefix sums of the matrices' M in the fused row space
   int n_rows;                     // rows in the fused space (SwiGLU: M of gate)
@@ -301,7 +302,11 @@ nf4_gemv_kernel(const GemvArgs a) {
       yo[local] = __float2bfloat16(v);
     } else {
       if (a.extra[0] != nullptr) v += __bfloat162float(a.extra[0][unit]);
-      a.y[0][unit] = __float2bfloat16(v);
+      if (a.y32 != nullptr) {
+        a.y32[unit] = v;
+      } else {
+        a.y[0][unit] = __float2bfloat16(v);
+      }
     }
   };
 
@@ -466,6 +471,27 @@ extern "C" int chr_nf4_gemv(const chr_nf4_dev_t *w, const void *x, void *y, void
   a.packed[0] = w->packed;
   a.scale[0] = w->scale;
   a.y[0] = static_cast<__nv_bfloat16 *>(y);
+  a.extra[0] = static_cast<const __nv_bfloat16 *>(add);
+  a.rows_end[0] = a.rows_end[1] = a.rows_end[2] = w->M;
+  a.n_rows = w->M;
+  a.K = w->K;
+  a.K_pad = w->K_pad;
+  a.x = static_cast<const __nv_bfloat16 *>(x);
+  a.rms_w = static_cast<const __nv_bfloat16 *>(rms_w);
+  a.rms_eps = rms_eps;
+  return launch<0>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y, void *stream,
+                                const void *add, const void *rms_w, float rms_eps) {
+  if (w == nullptr || x == nullptr || y == nullptr) return kNull;
+  const int rc = check_matrix(w);
+  if (rc != kOk) return rc;
+  if (!aligned(w->packed, 16) || !aligned(x, 16) || !aligned(w->scale, 2)) return kAlign;
+  GemvArgs a{};
+  a.packed[0] = w->packed;
+  a.scale[0] = w->scale;
+  a.y32 = y;
   a.extra[0] = static_cast<const __nv_bfloat16 *>(add);
   a.rows_end[0] = a.rows_end[1] = a.rows_end[2] = w->M;
   a.n_rows = w->M;

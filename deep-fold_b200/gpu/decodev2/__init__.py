@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 from .arch import (CONFIGS, INTERNLM25_20B, MEDIUM_LLAMA, QWEN25_3B, QWEN25_14B, QWEN25_32B,
-                   TINY_INTERNLM, TINY_LLAMA, ArchSpec, with_max_seq)
+                   TINY_INTERNLM, TINY_LLAMA, ArchSpec, shard_spec, with_max_seq)
 from .embed import PackedEmbed, bind_embed, gather_embed
 from .graph import GreedyGraph, capture_greedy
 from .linear import (DeviceLayer, DeviceLinear, DeviceWeights, linear_backend, nf4_linear,
@@ -15,6 +15,7 @@ from .session import DecodeV2Loop, Generation
 from .state import Arena, DecodeState, GraphSafeKV
 from .step import forward_decode, greedy_decode, set_fuse_rms, teacher_force_token
 from .synth import Nf4Matrix, SynthLayer, SynthModel, build
+from .tp import Comm, shard_weights
 
 __all__ = [
     "ArchSpec", "Arena", "CONFIGS", "DecodeState", "DecodeV2Loop", "DeviceLayer", "DeviceLinear",
@@ -24,5 +25,5 @@ __all__ = [
     "capture_greedy", "consume_prompt", "forward_decode", "forward_prefill", "gather_embed",
     "generate", "greedy_decode", "linear_backend", "nf4_linear", "prefill_chunk_width",
     "rope_tables_numpy", "rope_tables_torch", "set_fuse_rms", "set_linear_backend",
-    "teacher_force_token", "with_max_seq",
+    "teacher_force_token", "with_max_seq", "Comm", "shard_spec", "shard_weights",
 ]

@@ -21,6 +21,8 @@ __all__ = [
     "QWEN25_32B",
     "CONFIGS",
     "with_max_seq",
+    "shard_spec",
+    "group_range",
 ]
 
 _FAMILIES = ("llama_swiglu", "internlm_gqa")
@@ -46,19 +48,26 @@ class ArchSpec:
     eos_id: int = 2
     tied_embed: bool = False
     qkv_bias: bool = False
+    #: tensor-parallel degree this spec is one shard of; ``n_q``, ``n_kv`` and
+    #: ``intermediate`` are the LOCAL sizes when ``tp > 1`` (``hidden`` and ``vocab`` stay
+    #: global: the residual stream and the gathered logits are replicated).
+    tp: int = 1
+    #: ranks that hold a copy of the same kv head (``tp > n_kv`` of the full model)
+    kv_replicas: int = 1
 
     def __post_init__(self) -> None:
         if self.family not in _FAMILIES:
             raise ValueError(f"unsupported family {self.family!r}")
         if self.n_layers < 1 or self.max_seq < 2:
             raise ValueError("need at least one layer and max_seq>=2")
-        if self.hidden != self.n_q * self.head_dim:
-            raise ValueError(f"hidden {self.hidden} != n_q*head_dim {self.n_q * self.head_dim}")
+        if self.hidden != self.n_q * self.head_dim * self.tp:
+            raise ValueError(
+                f"hidden {self.hidden} != n_q*head_dim*tp {self.n_q * self.head_dim * self.tp}")
         if self.n_q % self.n_kv:
             raise ValueError(f"n_q={self.n_q} is not a multiple of n_kv={self.n_kv}")
         if self.head_dim % 2:
             raise ValueError("RoPE needs even head_dim")
-        if self.hidden % 64 or self.intermediate % 64:
+        if self.hidden % 64 or self.intermediate % 64:  # row-split shards keep whole NF4 groups
             raise ValueError("hidden and intermediate must be multiples of NF4 group 64")
         if not 0 <= self.eos_id < self.vocab:
             raise ValueError(f"eos_id {self.eos_id} out of vocab {self.vocab}")
@@ -100,6 +109,43 @@ class ArchSpec:
         shapes = self.linear_shapes()
         layer = sum(per(*mk) for name, mk in shapes.items() if name != "lm_head")
         return self.n_layers * layer + per(*shapes["lm_head"])
+
+
+def group_range(total: int, world: int, rank: int) -> tuple[int, int]:
+    """Elements ``[lo, hi)`` of a ``total``-wide axis owned by ``rank`` when the axis
+    is cut at NF4 group boundaries (multiples of 64); the first ranks take the
+    remainder groups, so shards may differ by one group."""
+    groups = total // 64
+    base, rem = divmod(groups, world)
+    lo = rank * base + min(rank, rem)
+    return lo * 64, (lo + base + (1 if rank < rem else 0)) * 64
+
+
+def shard_spec(spec: ArchSpec, world: int, rank: int = 0) -> ArchSpec:
+    """The per-rank spec of ``spec`` under tensor parallelism of degree ``world``.
+
+    Query heads, the MLP width and the lm_head rows are divided; kv heads are divided
+    when there are enough of them and otherwise replicated (each rank keeps the one
+    kv head its query heads attend to). The MLP width is cut at NF4 group
+    boundaries, so it may differ by 64 between ranks."""
+    world = int(world)
+    if spec.tp != 1:
+        raise ValueError("spec is already a shard")
+    if world == 1:
+        return spec
+    if spec.n_q % world or spec.vocab % world or spec.intermediate // 64 < world:
+        raise ValueError(f"{spec.name}: n_q / vocab / intermediate do not divide by tp={world}")
+    if spec.n_kv % world == 0:
+        n_kv, reps = spec.n_kv // world, 1
+    elif world % spec.n_kv == 0:
+        n_kv, reps = 1, world // spec.n_kv
+    else:
+        raise ValueError(f"{spec.name}: n_kv={spec.n_kv} and tp={world} do not nest")
+    if (spec.n_q // world) % n_kv:
+        raise ValueError("local query heads must be a multiple of local kv heads")
+    lo, hi = group_range(spec.intermediate, world, rank)
+    return replace(spec, n_q=spec.n_q // world, n_kv=n_kv, intermediate=hi - lo,
+                   tp=world, kv_replicas=reps)
 
 
 def with_max_seq(spec: ArchSpec, max_seq: int) -> ArchSpec:

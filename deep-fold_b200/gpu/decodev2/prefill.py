@@ -55,6 +55,15 @@ def _attend(q, k, v, spec: ArchSpec, mask) -> torch.Tensor:
     return a.squeeze(0).permute(1, 0, 2).reshape(n, spec.q_dim)
 
 
+def _reduced(state: DecodeState, partial: torch.Tensor) -> torch.Tensor:
+    """Sum a row-split linear's output over the tensor-parallel ranks (FP32 on the wire)."""
+    if state.spec.tp == 1:
+        return partial
+    acc = partial.float()
+    state.comm.all_reduce_sum(acc)
+    return acc.to(partial.dtype)
+
+
 def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch.Tensor,
                     start: int, *, logits: bool = True) -> None:
     """Teacher-force ``token_ids`` into KV slots ``start..start+n-1``."""
@@ -79,14 +88,19 @@ def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch
         k = apply_rope_torch(k, cos, sin)
         state.kv.write_range(li, start, k, v)
         k_all, v_all = state.kv.view(li, seq)
-        x = x + nf4_linear(layer.o, _attend(q, k_all, v_all, spec, mask))
+        x = x + _reduced(state, nf4_linear(layer.o, _attend(q, k_all, v_all, spec, mask)))
         h = F.rms_norm(x, layer.norm2.shape, layer.norm2, spec.rms_eps)
-        x = x + nf4_linear(layer.down, F.silu(nf4_linear(layer.gate, h)) * nf4_linear(layer.up, h))
+        x = x + _reduced(state, nf4_linear(
+            layer.down, F.silu(nf4_linear(layer.gate, h)) * nf4_linear(layer.up, h)))
     state.position.fill_(seq)
     state.valid_len.fill_(seq)
     if not logits:
         return
     hidden = F.rms_norm(x[-1:], weights.final_norm.shape, weights.final_norm, spec.rms_eps)
     out = nf4_linear(weights.lm_head, hidden)
-    state.arena.logits[0].copy_(out.reshape(-1))
-    state.next_token.copy_(out.argmax(dim=-1).reshape(()).to(dtype=torch.int64))
+    if spec.tp > 1:
+        state.comm.all_gather_into(state.arena.logits.view(-1), out.reshape(-1).contiguous())
+        out = state.arena.logits
+    else:
+        state.arena.logits[0].copy_(out.reshape(-1))
+    state.next_token.copy_(out.reshape(-1).argmax(dim=-1).reshape(()).to(dtype=torch.int64))

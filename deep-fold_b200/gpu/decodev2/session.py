@@ -70,8 +70,10 @@ class DecodeV2Loop:
         self._graph = None
 
     @classmethod
-    def from_weights(cls, weights: DeviceWeights, *, dtype: torch.dtype = torch.bfloat16) -> "DecodeV2Loop":
-        return cls(DecodeState.allocate(weights.spec, weights.embed, dtype=dtype), weights)
+    def from_weights(cls, weights: DeviceWeights, *, dtype: torch.dtype = torch.bfloat16,
+                     comm=None) -> "DecodeV2Loop":
+        """``weights`` may be a tensor-parallel shard (``weights.spec.tp > 1``) with its ``comm``."""
+        return cls(DecodeState.allocate(weights.spec, weights.embed, dtype=dtype, comm=comm), weights)
 
     @property
     def device(self) -> torch.device:

@@ -93,6 +93,8 @@ class Arena:
     attn_ws: torch.Tensor
     pick_scratch: torch.Tensor
     status: torch.Tensor
+    partial: torch.Tensor        # FP32 [hidden]: row-split partial sums under tensor parallelism
+    logits_local: torch.Tensor   # bf16 [vocab / tp]: this rank's lm_head rows
 
     @classmethod
     def allocate(cls, spec: ArchSpec, *, device, dtype: torch.dtype = torch.bfloat16) -> "Arena":
@@ -113,6 +115,8 @@ class Arena:
             ),
             pick_scratch=torch.zeros(16, dtype=torch.uint8, device=device),
             status=torch.zeros((), dtype=torch.int32, device=device),
+            partial=torch.zeros(spec.hidden, dtype=torch.float32, device=device),
+            logits_local=z(1, spec.vocab // spec.tp),
         )
 
 
@@ -130,10 +134,12 @@ class DecodeState:
     sin: torch.Tensor
     embed: "torch.Tensor | PackedEmbed"
     eos_id: torch.Tensor
+    comm: object = None          # tp.Comm; None = single GPU
 
     @classmethod
     def allocate(cls, spec: ArchSpec, embed, *, device=None, dtype: torch.dtype = torch.bfloat16,
-                 cos: torch.Tensor | None = None, sin: torch.Tensor | None = None) -> "DecodeState":
+                 cos: torch.Tensor | None = None, sin: torch.Tensor | None = None,
+                 comm=None) -> "DecodeState":
         if isinstance(embed, PackedEmbed):
             if embed.shape != (spec.vocab, spec.hidden):
                 raise ValueError(f"embed shape {embed.shape} != {(spec.vocab, spec.hidden)}")
@@ -147,6 +153,8 @@ class DecodeState:
         device = torch.device(device)
         if device.type != "cuda":
             raise RuntimeError("the resident executor is CUDA-only (no CPU path)")
+        if spec.tp > 1 and (comm is None or comm.world != spec.tp):
+            raise ValueError(f"a tp={spec.tp} shard needs a communicator of that size")
         valid_len = torch.zeros((), dtype=torch.int32, device=device)
         if cos is None or sin is None:
             cos, sin = rope_tables_torch(
@@ -169,6 +177,7 @@ class DecodeState:
             sin=sin.contiguous(),
             embed=held,
             eos_id=torch.tensor(spec.eos_id, dtype=torch.int64, device=device),
+            comm=comm,
         )
 
     @property

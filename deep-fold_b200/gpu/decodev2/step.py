@@ -14,8 +14,8 @@ from __future__ import annotations
 
 import torch
 
-from gpu.nf4 import (ATTN_SPLIT, nf4_attn, nf4_gemv, nf4_pick_commit, nf4_qkv, nf4_rms,
-                     nf4_swiglu)
+from gpu.nf4 import (ATTN_SPLIT, nf4_attn, nf4_gemv, nf4_gemv_f32, nf4_pick_commit, nf4_qkv,
+                     nf4_rms, nf4_swiglu)
 
 from .embed import PackedEmbed
 from .linear import DeviceLayer, DeviceLinear, DeviceWeights
@@ -72,12 +72,19 @@ def _qkv(state: DecodeState, layer: DeviceLayer) -> None:
     ar.v.view(spec.n_kv, spec.head_dim).copy_(grouped[:, -1])
 
 
-def _accumulate(mat: DeviceLinear, src: torch.Tensor, dest: torch.Tensor) -> None:
-    """``dest += W @ src`` in one launch (residual fused into the GEMV epilogue)."""
-    nf4_gemv(mat.packed, mat.scale, src.reshape(mat.K), mat.M, mat.K, mat.K_pad,
-             dest.view(-1), dest.view(-1))
-    if mat.bias is not None:
-        dest.view(-1).add_(mat.bias.to(dtype=dest.dtype))
+def _accumulate(state: DecodeState, mat: DeviceLinear, src: torch.Tensor, dest: torch.Tensor) -> None:
+    """``dest += W @ src``. Single GPU: one launch, residual fused into the GEMV
+    epilogue. Row-split shard: FP32 partial -> sum all-reduce -> one rounded add."""
+    if state.spec.tp == 1:
+        nf4_gemv(mat.packed, mat.scale, src.reshape(mat.K), mat.M, mat.K, mat.K_pad,
+                 dest.view(-1), dest.view(-1))
+        if mat.bias is not None:
+            dest.view(-1).add_(mat.bias.to(dtype=dest.dtype))
+        return
+    part = state.arena.partial
+    nf4_gemv_f32(mat.packed, mat.scale, src.reshape(mat.K), mat.M, mat.K, mat.K_pad, part, mat.bias)
+    state.comm.all_reduce_sum(part)
+    dest.view(-1).add_(part)
 
 
 def forward_decode(state: DecodeState, weights: DeviceWeights) -> None:
@@ -87,16 +94,21 @@ def forward_decode(state: DecodeState, weights: DeviceWeights) -> None:
         _qkv(state, layer)
         nf4_attn(ar.q, state.kv.k[li], state.kv.v[li], ar.attn, state.valid_len, spec.attn_scale,
                  ar.attn_ws, ATTN_SPLIT, ar.k, ar.v, state.cos, state.sin, state.position)
-        _accumulate(layer.o, ar.attn, ar.x)
+        _accumulate(state, layer.o, ar.attn, ar.x)
         x, rms_w = _normed(state, layer.norm2)
         g, u = layer.gate, layer.up
         nf4_swiglu(g.packed, g.scale, u.packed, u.scale, x, g.M, g.K, g.K_pad,
                    ar.down_in.view(-1), rms_w, spec.rms_eps)
-        _accumulate(layer.down, ar.down_in, ar.x)
+        _accumulate(state, layer.down, ar.down_in, ar.x)
     x, rms_w = _normed(state, weights.final_norm)
     head = weights.lm_head
-    nf4_gemv(head.packed, head.scale, x, head.M, head.K, head.K_pad, ar.logits.view(-1),
-             head.bias, rms_w, spec.rms_eps)
+    if spec.tp == 1:
+        nf4_gemv(head.packed, head.scale, x, head.M, head.K, head.K_pad, ar.logits.view(-1),
+                 head.bias, rms_w, spec.rms_eps)
+    else:  # vocabulary slice per rank, gathered in rank order into the full logits
+        nf4_gemv(head.packed, head.scale, x, head.M, head.K, head.K_pad,
+                 ar.logits_local.view(-1), head.bias, rms_w, spec.rms_eps)
+        state.comm.all_gather_into(ar.logits.view(-1), ar.logits_local.view(-1))
 
 
 def greedy_decode(state: DecodeState, weights: DeviceWeights) -> None:

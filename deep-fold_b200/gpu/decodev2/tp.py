@@ -1,0 +1,132 @@
+"""Tensor-parallel sharding of the NF4 decoder over the GPUs of one box.
+
+Not in the reference (single GPU). Column-split (rows of W, contiguous slices of
+the packed bytes, nothing repacked): q / k / v by head, InternLM's fused wqkv by kv
+group, gate, up, lm_head. Row-split (K ranges that are multiples of 64, so no NF4
+group straddles ranks; bytes are copied into a contiguous per-rank blob, never
+re-quantized): o, down. One sum all-reduce of the FP32 partial per row-split
+layer and one all-gather of the logits slices per token, both issued on the
+capture stream so they become nodes of the step graph.
+
+``Comm`` wraps ``torch.distributed``; the same code runs with the NCCL backend on
+GPUs and with gloo on CPU (sharding arithmetic and the collectives' semantics are
+tested there).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .arch import ArchSpec, group_range, shard_spec
+from .linear import DeviceLayer, DeviceLinear, DeviceWeights
+
+__all__ = ["Comm", "shard_linear_cols", "shard_linear_rows", "shard_weights", "kv_head_rows"]
+
+
+@dataclass
+class Comm:
+    """Rank / world plus the two collectives the step needs."""
+
+    rank: int = 0
+    world: int = 1
+    group: object | None = None
+
+    @classmethod
+    def from_env(cls) -> "Comm":
+        import torch.distributed as dist
+
+        if dist.is_available() and dist.is_initialized():
+            return cls(dist.get_rank(), dist.get_world_size(), None)
+        return cls()
+
+    def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def all_gather_into(self, out: torch.Tensor, part: torch.Tensor) -> torch.Tensor:
+        """``out`` (world * part.numel()) <- every rank's ``part`` in rank order."""
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(out, part, group=self.group)
+        else:
+            out.copy_(part.reshape(out.shape))
+        return out
+
+
+def _rows(mat: DeviceLinear, lo: int, hi: int) -> DeviceLinear:
+    """Rows lo..hi of a matrix: a view of the packed bytes, no copy."""
+    bias = None if mat.bias is None else mat.bias[lo:hi].contiguous()
+    return DeviceLinear(mat.packed[lo:hi], mat.scale[lo:hi], hi - lo, mat.K, mat.K_pad, bias)
+
+
+def shard_linear_cols(mat: DeviceLinear, rank: int, world: int) -> DeviceLinear:
+    """Output rows ``[rank*M/world, (rank+1)*M/world)``."""
+    if mat.M % world:
+        raise ValueError(f"M={mat.M} does not divide by {world}")
+    step = mat.M // world
+    return _rows(mat, rank * step, (rank + 1) * step)
+
+
+def shard_linear_rows(mat: DeviceLinear, rank: int, world: int,
+                      k_range: tuple[int, int] | None = None) -> DeviceLinear:
+    """Input range ``k_range`` (default: the rank's even share) re-laid as its own
+    matrix. The range must start and end on NF4 group boundaries. The bias (if any)
+    stays on rank 0 only, so that the all-reduced sum carries it once."""
+    lo, hi = k_range if k_range is not None else group_range(mat.K, world, rank)
+    if lo % 64 or hi % 64 or not 0 <= lo < hi <= mat.K:
+        raise ValueError(f"K range {lo}..{hi} of {mat.K} is not made of whole NF4 groups")
+    packed = mat.packed[:, lo // 2:hi // 2].contiguous()
+    scale = mat.scale[:, lo // 64:hi // 64].contiguous()
+    return DeviceLinear(packed, scale, mat.M, hi - lo, hi - lo, mat.bias if rank == 0 else None)
+
+
+def kv_head_rows(full: ArchSpec, rank: int, world: int) -> tuple[int, int]:
+    """Row range of this rank's kv heads inside a full k or v projection."""
+    hd = full.head_dim
+    if full.n_kv % world == 0:
+        per = full.n_kv // world
+        return rank * per * hd, (rank + 1) * per * hd
+    head = rank // (world // full.n_kv)
+    return head * hd, (head + 1) * hd
+
+
+def _shard_wqkv(mat: DeviceLinear, full: ArchSpec, rank: int, world: int) -> DeviceLinear:
+    """InternLM packing [n_kv, n_rep + 2, hd]: kv groups are contiguous row blocks."""
+    if full.n_kv % world:
+        raise ValueError("fused wqkv needs n_kv divisible by the tensor-parallel degree")
+    group = (full.n_rep + 2) * full.head_dim
+    per = full.n_kv // world
+    return _rows(mat, rank * per * group, (rank + 1) * per * group)
+
+
+def shard_weights(weights: DeviceWeights, rank: int, world: int) -> DeviceWeights:
+    """This rank's shard of a full model (views where possible)."""
+    full = weights.spec
+    if world == 1:
+        return weights
+    local = shard_spec(full, world, rank)
+    mlp = group_range(full.intermediate, world, rank)
+    layers = []
+    for ly in weights.layers:
+        q = k = v = wqkv = None
+        if ly.wqkv is not None:
+            wqkv = _shard_wqkv(ly.wqkv, full, rank, world)
+        else:
+            q = shard_linear_cols(ly.q, rank, world)
+            lo, hi = kv_head_rows(full, rank, world)
+            k, v = _rows(ly.k, lo, hi), _rows(ly.v, lo, hi)
+        layers.append(DeviceLayer(
+            ly.norm1, ly.norm2, q, k, v, wqkv,
+            shard_linear_rows(ly.o, rank, world),
+            _rows(ly.gate, *mlp),
+            _rows(ly.up, *mlp),
+            shard_linear_rows(ly.down, rank, world, mlp),
+        ))
+    return DeviceWeights(local, weights.embed, weights.final_norm,
+                         shard_linear_cols(weights.lm_head, rank, world), layers)

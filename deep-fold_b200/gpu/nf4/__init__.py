@@ -31,6 +31,7 @@ __all__ = [
     "nf4_gemm_rows",
     "nf4_gemm_status",
     "nf4_gemv",
+    "nf4_gemv_f32",
     "nf4_pick_commit",
     "nf4_plan",
     "nf4_qkv",
@@ -277,6 +278,35 @@ def nf4_gemv(
     _lib.check(rc, "chr_nf4_gemv")
     del keep
     return y
+
+
+def nf4_gemv_f32(
+    packed: torch.Tensor,
+    scale: torch.Tensor,
+    x: torch.Tensor,
+    M: int,  # noqa: N803
+    K: int,  # noqa: N803
+    K_pad: int,  # noqa: N803
+    out: torch.Tensor,
+    add: torch.Tensor | None = None,
+    rms_w: torch.Tensor | None = None,
+    rms_eps: float = 1e-6,
+) -> torch.Tensor:
+    """:func:`nf4_gemv` with the FP32 sum kept unrounded in ``out`` (float32, numel >= M)."""
+    dev, keep = _matrix(packed, scale, M, K, K_pad)
+    xk = _kvec(x, int(K))
+    if not out.is_cuda or out.dtype is not torch.float32 or not out.is_contiguous():
+        _fail("out must be contiguous CUDA float32")
+    if out.numel() < int(M):
+        _fail("out too small")
+    add_t = _opt_bf16(add, int(M), "add", exact=False)
+    rms_t = _opt_bf16(rms_w, int(K), "rms_w", exact=True)
+    rc = _lib.load().chr_nf4_gemv_f32(
+        ctypes.byref(dev), _ptr(xk), _ptr(out), _stream(), _ptr(add_t), _ptr(rms_t), float(rms_eps)
+    )
+    _lib.check(rc, "chr_nf4_gemv_f32")
+    del keep
+    return out
 
 
 def nf4_qkv(

@@ -59,6 +59,7 @@ SIGNATURES = {
     ),
     "chr_nf4_set_tuning": (None, [c_int32, c_int32, c_int32]),
     "chr_nf4_gemv": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
+    "chr_nf4_gemv_f32": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
     "chr_nf4_gemv_qkv": (
         c_int,
         [_DEV, _DEV, _DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -132,6 +132,12 @@ int chr_nf4_rms(const void *x, const void *w, void *y, int32_t n, float eps,
 /* Library identification: "chr_nf4 sm_100a <build tag>". */
 const char *chr_nf4_version(void);
 
+/* chr_nf4_gemv with the FP32 sum stored unrounded (y: device float [M]): the
+ * partial result of a row-split (tensor-parallel) linear, to be summed across
+ * ranks before the single bf16 rounding. add: optional bf16 [M] (e.g. a bias). */
+int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y, void *stream,
+                     const void *add, const void *rms_w, float rms_eps);
+
 /* Wide GEMM on activation rows: y_rows[N, M] = bf16( x_rows[N, K] . dequant(W)^T ),
  * the layout activations already have ([tokens, features], K contiguous), so no
  * transposes on either side and any N >= 1 in one call (tiled 16..256 columns per
