@@ -201,6 +201,7 @@ def run_ours(args, spec) -> None:
     gen = torch.Generator().manual_seed(2)
     prompt = torch.randint(0, spec.vocab, (args.prompt,), generator=gen).tolist()
     loop.warmup(prompt=8, tokens=4)
+    fused_why = loop.enable_fused_step() if args.fused else "default"
     mode = loop.capture_graphs()
     if mode != "decodev2":
         raise SystemExit(f"graph capture failed: {loop.graph_error}")
@@ -307,9 +308,13 @@ def run_ours(args, spec) -> None:
         if dist is not None:
             dist.destroy_process_group()
         return
-    launches_per_step = 1 + spec.n_layers * 5 + 2
-    if spec.family == "internlm_gqa":
-        launches_per_step += 0  # the split copies are torch kernels, not counted
+    if loop.fused:
+        launches_per_step = 1  # the whole step is one persistent kernel
+        status = loop._fused.status()
+        if status != 0:
+            raise SystemExit(f"persistent step reported status {status}")
+    else:
+        launches_per_step = 1 + spec.n_layers * 5 + 2
     step_bytes = full_spec.packed_bytes_per_token()
     line = {
         "metric": METRIC, "value": args.steps / (dev_ms / 1e3), "unit": UNIT, "n_gpus": world,
@@ -323,11 +328,24 @@ def run_ours(args, spec) -> None:
                 "d2h_bytes_per_step": 8},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clk,
-        "roofline": {"kernel": "nf4_gemv_kernel<swiglu> (gate+up, fused RMSNorm)", "bound": "hbm",
-                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": achieved / peak, "bytes_per_launch": per_launch, "us_per_launch": k_us,
-                     "traffic": None},
     }
+    gemv_roof = {"kernel": "nf4_gemv_kernel<swiglu> (gate+up, fused RMSNorm)", "bound": "hbm",
+                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                 "frac": achieved / peak, "bytes_per_launch": per_launch, "us_per_launch": k_us,
+                 "traffic": None}
+    if loop.fused:
+        # one launch = one token: every packed weight byte and scale is read once
+        step_us = dev_ms / args.steps * 1e3
+        line["roofline"] = {"kernel": "decode_step_kernel (whole greedy step, persistent)",
+                            "bound": "hbm", "achieved": step_bytes / (step_us * 1e-6) / 1e9,
+                            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                            "frac": step_bytes / (step_us * 1e-6) / 1e9 / peak,
+                            "bytes_per_launch": step_bytes, "us_per_launch": step_us,
+                            "traffic": None}
+        line["gemv_alone"] = gemv_roof
+    else:
+        line["roofline"] = gemv_roof
+        line["step_mode"] = f"launch chain ({fused_why})"
     if not args.no_cpu:
         cb = cpu_layer_sample(full_spec)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -345,6 +363,9 @@ def main() -> None:
     ap.add_argument("--model", default="qwen2.5-3b-arch")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--fused", action="store_true",
+                    help="run the step as one persistent kernel instead of the graph of one launch "
+                         "per operation (same bits; slower on the 3B shapes as measured)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     from gpu.decodev2.arch import CONFIGS

@@ -6,7 +6,7 @@
 // (kv head, sequence split) pair and serves every query head of that kv head, so
 // a cache row is read once per group instead of once per query head.
 
-#include "nf4_common.cuh"
+#include "attn_core.cuh"
 
 namespace chr {
 namespace {
@@ -72,267 +72,21 @@ __global__ void rope_kv_kernel(__nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__r
 // ----------------------------------------------------------------------------
 // GQA decode attention  (reference: gpu/nf4/nf4_gemv.cu:558-727)
 // ----------------------------------------------------------------------------
-constexpr int kAttnWarps = 8;
-constexpr int kAttnMaxSplit = 16;  // splits actually used: min(n_split, 16)
-constexpr int kAttnThreads = kAttnWarps * 32;
-constexpr float kNegInit = -1.0e30f;
-
 // Arrival counters for the merge-by-last-CTA step: one per (kv head, head chunk).
 // Zero at load, and the last CTA of a group puts its counter back to zero, so a
 // launch leaves them as it found them. Launches of the attention kernel that
 // overlap on the device (different streams) would share them and must not.
-constexpr int kMaxAttnGroups = 1024;
 __device__ unsigned int g_attn_arrivals[kMaxAttnGroups];
 
-// P: bf16 pairs per lane (hd <= 64*P). H: query heads served by one CTA.
+// Grid: (splits, kv heads, head chunks); the core is in attn_core.cuh.
 template <int P, int H>
-__global__ void __launch_bounds__(kAttnThreads)
-attn_split_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *k_cache,
-                  const __nv_bfloat16 *v_cache, __nv_bfloat16 *__restrict__ out,
-                  float *m_s, float *l_s, float *o_s,
-                  const int32_t *__restrict__ valid_len,
-                  const __nv_bfloat16 *__restrict__ k_act, const __nv_bfloat16 *__restrict__ v_act,
-                  const __nv_bfloat16 *__restrict__ cos, const __nv_bfloat16 *__restrict__ sin,
-                  const int64_t *__restrict__ position, int n_q, int n_kv, int hd, int n_split,
-                  int max_seq, float scale) {
-  __shared__ float qrot[H][64 * P];
-  __shared__ float krot[64 * P];
-  __shared__ float vcur[64 * P];
-  __shared__ float sm_m[kAttnWarps][H];
-  __shared__ float sm_l[kAttnWarps][H];
-  __shared__ float sm_o[kAttnWarps][H][64 * P];
-  __shared__ bool is_last;
-
-  const int split = blockIdx.x;
-  const int kvh = blockIdx.y;
-  const int n_rep = n_q / n_kv;
-  const int h_first = kvh * n_rep + blockIdx.z * H;  // first query head of this CTA
-  const int nh = min(H, n_rep - static_cast<int>(blockIdx.z) * H);
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int warp = tid >> 5;
-  const int half = hd >> 1;
-
+__global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const AttnArgs a) {
+  __shared__ AttnSmem<P, H> sm;
   pdl_trigger();
   pdl_wait();  // q, k_act, v_act, position and valid_len come from earlier kernels
-  int vl = *valid_len;
-  vl = vl < 0 ? 0 : (vl > max_seq ? max_seq : vl);
-
-  long long pos = -1;
-  bool fuse_kv = false;
-  const bool have_rope = cos != nullptr && sin != nullptr && position != nullptr;
-  if (have_rope) {
-    pos = *position;
-    if (pos < 0 || pos >= max_seq) pos = -1;
-  }
-  if (pos >= 0) {
-    const __nv_bfloat16 *c = cos + static_cast<size_t>(pos) * hd;
-    const __nv_bfloat16 *s = sin + static_cast<size_t>(pos) * hd;
-    for (int i = tid; i < nh * half; i += kAttnThreads) {
-      const int h = i / half;
-      const int d = i - h * half;
-      const __nv_bfloat16 *qh = q + static_cast<size_t>(h_first + h) * hd;
-      const float lo = __bfloat162float(qh[d]);
-      const float hi = __bfloat162float(qh[d + half]);
-      qrot[h][d] = lo * __bfloat162float(c[d]) + (-hi) * __bfloat162float(s[d]);
-      qrot[h][d + half] = hi * __bfloat162float(c[d + half]) + lo * __bfloat162float(s[d + half]);
-    }
-    if (k_act != nullptr && v_act != nullptr) {
-      fuse_kv = true;
-      const __nv_bfloat16 *ka = k_act + static_cast<size_t>(kvh) * hd;
-      const __nv_bfloat16 *va = v_act + static_cast<size_t>(kvh) * hd;
-      for (int d = tid; d < half; d += kAttnThreads) {
-        const float lo = __bfloat162float(ka[d]);
-        const float hi = __bfloat162float(ka[d + half]);
-        krot[d] = lo * __bfloat162float(c[d]) + (-hi) * __bfloat162float(s[d]);
-        krot[d + half] = hi * __bfloat162float(c[d + half]) + lo * __bfloat162float(s[d + half]);
-      }
-      for (int d = tid; d < hd; d += kAttnThreads) vcur[d] = __bfloat162float(va[d]);
-    }
-  } else {
-    for (int i = tid; i < nh * hd; i += kAttnThreads) {
-      const int h = i / hd;
-      const int d = i - h * hd;
-      qrot[h][d] = __bfloat162float(q[static_cast<size_t>(h_first + h) * hd + d]);
-    }
-  }
-  __syncthreads();
-
-  // One CTA per kv head stores the new cache row; every CTA attends the current
-  // token from the FP32 values above, never from the row being written.
-  if (fuse_kv && blockIdx.z == 0 && split == static_cast<int>(pos % n_split)) {
-    const size_t off = (static_cast<size_t>(pos) * n_kv + kvh) * hd;
-    __nv_bfloat16 *kc = const_cast<__nv_bfloat16 *>(k_cache) + off;
-    __nv_bfloat16 *vc = const_cast<__nv_bfloat16 *>(v_cache) + off;
-    const __nv_bfloat16 *va = v_act + static_cast<size_t>(kvh) * hd;
-    for (int d = tid; d < hd; d += kAttnThreads) {
-      kc[d] = __float2bfloat16(krot[d]);
-      vc[d] = va[d];
-    }
-  }
-
-  // Lane owns elements d = 2*lane + 64*p (+0, +1).
-  float qreg[H][2 * P];
-#pragma unroll
-  for (int h = 0; h < H; ++h) {
-#pragma unroll
-    for (int p = 0; p < P; ++p) {
-      const int d = 2 * lane + 64 * p;
-      const bool live = h < nh && d < hd;
-      qreg[h][2 * p] = live ? qrot[h][d] : 0.f;
-      qreg[h][2 * p + 1] = live ? qrot[h][d + 1] : 0.f;
-    }
-  }
-
-  float m[H], l[H], acc[H][2 * P];
-#pragma unroll
-  for (int h = 0; h < H; ++h) {
-    m[h] = kNegInit;
-    l[h] = 0.f;
-#pragma unroll
-    for (int e = 0; e < 2 * P; ++e) acc[h][e] = 0.f;
-  }
-
-  // Token loop, one token ahead: the next row's K/V are in flight while this one
-  // is scored. Row t of this warp: split + warp*n_split + i*4*n_split.
-  const int t_step = kAttnWarps * n_split;
-  uint32_t kb[P], vb[P], kb_n[P], vb_n[P];
-  auto fetch = [&](int t, uint32_t (&kk)[P], uint32_t (&vv)[P]) {
-    const size_t row = (static_cast<size_t>(t) * n_kv + kvh) * hd;
-#pragma unroll
-    for (int p = 0; p < P; ++p) {
-      const int d = 2 * lane + 64 * p;
-      const bool live = t < vl && d < hd;
-      kk[p] = live ? __ldg(reinterpret_cast<const uint32_t *>(k_cache + row + d)) : 0u;
-      vv[p] = live ? __ldg(reinterpret_cast<const uint32_t *>(v_cache + row + d)) : 0u;
-    }
-  };
-  int t = split + warp * n_split;
-  fetch(t, kb, vb);
-  for (; t < vl; t += t_step) {
-    fetch(t + t_step, kb_n, vb_n);
-    float kk[2 * P], vv[2 * P];
-    const bool cur = fuse_kv && t == pos;
-#pragma unroll
-    for (int p = 0; p < P; ++p) {
-      const int d = 2 * lane + 64 * p;
-      if (cur && d < hd) {
-        kk[2 * p] = krot[d];
-        kk[2 * p + 1] = krot[d + 1];
-        vv[2 * p] = vcur[d];
-        vv[2 * p + 1] = vcur[d + 1];
-      } else {
-        kk[2 * p] = bf16_lo(kb[p]);
-        kk[2 * p + 1] = bf16_hi(kb[p]);
-        vv[2 * p] = bf16_lo(vb[p]);
-        vv[2 * p + 1] = bf16_hi(vb[p]);
-      }
-    }
-    float dots[H];
-#pragma unroll
-    for (int h = 0; h < H; ++h) {
-      float dot = 0.f;
-#pragma unroll
-      for (int e = 0; e < 2 * P; ++e) dot = fmaf(qreg[h][e], kk[e], dot);
-      dots[h] = dot;
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-      for (int h = 0; h < H; ++h) dots[h] += __shfl_xor_sync(0xffffffffu, dots[h], off);
-    }
-#pragma unroll
-    for (int h = 0; h < H; ++h) {
-      const float dot = dots[h] * scale;
-      const float m2 = fmaxf(m[h], dot);
-      const float alpha = __expf(m[h] - m2);
-      const float ex = __expf(dot - m2);
-      l[h] = l[h] * alpha + ex;
-#pragma unroll
-      for (int e = 0; e < 2 * P; ++e) acc[h][e] = acc[h][e] * alpha + ex * vv[e];
-      m[h] = m2;
-    }
-#pragma unroll
-    for (int p = 0; p < P; ++p) {
-      kb[p] = kb_n[p];
-      vb[p] = vb_n[p];
-    }
-  }
-
-  // Combine the four warps, in warp order, into this split's (m, l, o).
-#pragma unroll
-  for (int h = 0; h < H; ++h) {
-    if (lane == 0) {
-      sm_m[warp][h] = m[h];
-      sm_l[warp][h] = l[h];
-    }
-#pragma unroll
-    for (int p = 0; p < P; ++p) {
-      const int d = 2 * lane + 64 * p;
-      sm_o[warp][h][d] = acc[h][2 * p];
-      sm_o[warp][h][d + 1] = acc[h][2 * p + 1];
-    }
-  }
-  __syncthreads();
-  for (int i = tid; i < nh * hd; i += kAttnThreads) {
-    const int h = i / hd;
-    const int d = i - h * hd;
-    float mm = kNegInit;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm_m[w][h]);
-    float ll = 0.f, oo = 0.f;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) {
-      const float a = __expf(sm_m[w][h] - mm);
-      ll += a * sm_l[w][h];
-      oo += a * sm_o[w][h][d];
-    }
-    const size_t slot = static_cast<size_t>(h_first + h) * n_split + split;
-    o_s[slot * hd + d] = oo;
-    if (d == 0) {
-      m_s[slot] = mm;
-      l_s[slot] = ll;
-    }
-  }
-
-  // The last CTA of this (kv head, head chunk) to arrive merges the splits.
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    unsigned int *ctr = &g_attn_arrivals[(kvh * gridDim.z + blockIdx.z) % kMaxAttnGroups];
-    const unsigned int seen = atomicAdd(ctr, 1u);
-    is_last = seen == static_cast<unsigned int>(n_split) - 1u;
-    if (is_last) *ctr = 0u;
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  // softmax weights of the splits, once per head: w[h][s] = exp(m_s - max) / sum
-  float *wts = &sm_o[0][0][0];  // the combine buffer is free again
-  for (int h = warp; h < nh; h += kAttnWarps) {
-    const size_t base = static_cast<size_t>(h_first + h) * n_split;
-    const float ms = lane < n_split ? __ldcg(m_s + base + lane) : kNegInit;
-    const float ls = lane < n_split ? __ldcg(l_s + base + lane) : 0.f;
-    const float mm = warp_max_xor(ms);
-    const float a = __expf(ms - mm);
-    const float ll = warp_sum_xor(a * ls);
-    if (lane < kAttnMaxSplit) wts[h * kAttnMaxSplit + lane] = ll > 0.f ? a / ll : 0.f;
-  }
-  __syncthreads();
-  for (int i = tid; i < nh * hd; i += kAttnThreads) {
-    const int h = i / hd;
-    const int d = i - h * hd;
-    const float *oh = o_s + static_cast<size_t>(h_first + h) * n_split * hd + d;
-    float v[kAttnMaxSplit];
-#pragma unroll
-    for (int sidx = 0; sidx < kAttnMaxSplit; ++sidx) {
-      v[sidx] = sidx < n_split ? __ldcg(oh + static_cast<size_t>(sidx) * hd) : 0.f;
-    }
-    float oo = 0.f;
-#pragma unroll
-    for (int sidx = 0; sidx < kAttnMaxSplit; ++sidx) oo += wts[h * kAttnMaxSplit + sidx] * v[sidx];
-    out[static_cast<size_t>(h_first + h) * hd + d] = __float2bfloat16(oo);
-  }
+  unsigned int *ctr = &g_attn_arrivals[(blockIdx.y * gridDim.z + blockIdx.z) % kMaxAttnGroups];
+  attn_item<P, H>(a, sm, blockIdx.x, blockIdx.y, blockIdx.z, ctr, threadIdx.x,
+                  [] { __syncthreads(); });
 }
 
 // ----------------------------------------------------------------------------
@@ -384,19 +138,6 @@ __global__ void embed_rows_kernel(const uint8_t *__restrict__ packed,
 // Greedy pick + commit  (reference: gpu/decodev2/step.py:182, state.py:98-103)
 // ----------------------------------------------------------------------------
 constexpr int kPickThreads = 256;
-
-__device__ __forceinline__ unsigned long long pick_key(uint32_t bf16_bits, int idx) {
-  uint32_t b = bf16_bits & 0xFFFFu;
-  uint32_t ord;
-  if ((b & 0x7FFFu) > 0x7F80u) {
-    ord = 0xFFFFu;  // NaN ranks above everything, as torch.argmax does
-  } else {
-    if (b == 0x8000u) b = 0u;  // -0 equals +0
-    ord = (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);
-  }
-  return (static_cast<unsigned long long>(ord) << 32) |
-         static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(idx));
-}
 
 __global__ void __launch_bounds__(kPickThreads)
 pick_commit_kernel(const __nv_bfloat16 *__restrict__ logits, int n, int64_t *next_token,
@@ -493,26 +234,35 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
   // partials the merging CTA has to read back.
   if (n_split > kAttnMaxSplit) n_split = kAttnMaxSplit;
   const int slots = n_q * n_split;
-  float *m_s = ws;
-  float *l_s = ws + slots;
-  float *o_s = ws + 2 * slots;
   const int n_rep = n_q / n_kv;
-  auto *qp = static_cast<const __nv_bfloat16 *>(q);
-  auto *kp = static_cast<const __nv_bfloat16 *>(k);
-  auto *vp = static_cast<const __nv_bfloat16 *>(v);
-  auto *vl = static_cast<const int32_t *>(valid_len);
-  auto *ka = static_cast<const __nv_bfloat16 *>(k_act);
-  auto *va = static_cast<const __nv_bfloat16 *>(v_act);
-  auto *cp = static_cast<const __nv_bfloat16 *>(cos);
-  auto *sp = static_cast<const __nv_bfloat16 *>(sin);
-  auto *pp = static_cast<const int64_t *>(position);
+  AttnArgs a{};
+  a.q = static_cast<const __nv_bfloat16 *>(q);
+  a.q_group_stride = n_rep * hd;
+  a.k_act = static_cast<const __nv_bfloat16 *>(k_act);
+  a.v_act = static_cast<const __nv_bfloat16 *>(v_act);
+  a.kv_act_stride = hd;
+  a.k_cache = static_cast<const __nv_bfloat16 *>(k);
+  a.v_cache = static_cast<const __nv_bfloat16 *>(v);
+  a.out = static_cast<__nv_bfloat16 *>(out);
+  a.m_s = ws;
+  a.l_s = ws + slots;
+  a.o_s = ws + 2 * slots;
+  a.valid_len = static_cast<const int32_t *>(valid_len);
+  a.cos = static_cast<const __nv_bfloat16 *>(cos);
+  a.sin = static_cast<const __nv_bfloat16 *>(sin);
+  a.position = static_cast<const int64_t *>(position);
+  a.n_q = n_q;
+  a.n_kv = n_kv;
+  a.hd = hd;
+  a.n_split = n_split;
+  a.max_seq = max_seq;
+  a.scale = scale;
 
 #define CHR_ATTN(PP, HH)                                                                       \
   launch_chain(attn_split_kernel<PP, HH>,                                                      \
                dim3(static_cast<unsigned>(n_split), static_cast<unsigned>(n_kv),               \
                     static_cast<unsigned>((n_rep + HH - 1) / HH)),                             \
-               dim3(kAttnThreads), 0, st, qp, kp, vp, static_cast<__nv_bfloat16 *>(out), m_s,  \
-               l_s, o_s, vl, ka, va, cp, sp, pp, n_q, n_kv, hd, n_split, max_seq, scale)
+               dim3(kAttnThreads), 0, st, a)
   cudaError_t e;
   if (hd <= 64) {
     if (n_kv * ((n_rep + 7) / 8) > kMaxAttnGroups) return kDims;

@@ -181,4 +181,19 @@ __device__ __forceinline__ float warp_sumsq_bf16(const __nv_bfloat16 *__restrict
   return warp_sum_xor(acc);
 }
 
+// Greedy pick: a key that orders (logit, index) pairs so that the maximum key is the
+// argmax with the lowest index on ties; NaN ranks above everything, -0 equals +0.
+__device__ __forceinline__ unsigned long long pick_key(uint32_t bf16_bits, int idx) {
+  uint32_t b = bf16_bits & 0xFFFFu;
+  uint32_t ord;
+  if ((b & 0x7FFFu) > 0x7F80u) {
+    ord = 0xFFFFu;  // NaN ranks above everything, as torch.argmax does
+  } else {
+    if (b == 0x8000u) b = 0u;  // -0 equals +0
+    ord = (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);
+  }
+  return (static_cast<unsigned long long>(ord) << 32) |
+         static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(idx));
+}
+
 }  // namespace chr

@@ -5,6 +5,7 @@ from __future__ import annotations
 from .arch import (CONFIGS, INTERNLM25_20B, MEDIUM_LLAMA, QWEN25_3B, QWEN25_14B, QWEN25_32B,
                    TINY_INTERNLM, TINY_LLAMA, ArchSpec, shard_spec, with_max_seq)
 from .embed import PackedEmbed, bind_embed, gather_embed
+from .fused import FusedStep, fused_step_supported
 from .graph import GreedyGraph, capture_greedy
 from .linear import (DeviceLayer, DeviceLinear, DeviceWeights, linear_backend, nf4_linear,
                      set_linear_backend)
@@ -18,6 +19,8 @@ from .synth import Nf4Matrix, SynthLayer, SynthModel, build
 from .tp import Comm, shard_weights
 
 __all__ = [
+    "FusedStep",
+    "fused_step_supported",
     "ArchSpec", "Arena", "CONFIGS", "DecodeState", "DecodeV2Loop", "DeviceLayer", "DeviceLinear",
     "DeviceWeights", "Generation", "GraphSafeKV", "GreedyGraph", "INTERNLM25_20B", "MEDIUM_LLAMA",
     "Nf4Matrix", "PackedEmbed", "QWEN25_14B", "QWEN25_32B", "QWEN25_3B", "SynthLayer",

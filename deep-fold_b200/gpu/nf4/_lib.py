@@ -46,6 +46,30 @@ class ChrNf4Plan(Structure):
     ]
 
 
+class ChrNf4StepLayer(Structure):
+    """Mirror of ``chr_nf4_step_layer_t``."""
+
+    _fields_ = [(n, ChrNf4Dev) for n in ("q", "k", "v", "o", "gate", "up", "down")] + [
+        (n, c_void_p) for n in ("bq", "bk", "bv", "norm1", "norm2", "k_cache", "v_cache")
+    ]
+
+
+class ChrNf4Step(Structure):
+    """Mirror of ``chr_nf4_step_t``."""
+
+    _fields_ = (
+        [(n, c_int32) for n in ("n_layers", "hidden", "intermediate", "n_q", "n_kv", "head_dim",
+                                "max_seq", "vocab", "n_split", "fused_qkv", "commit")]
+        + [("rms_eps", c_float), ("attn_scale", c_float), ("eos", c_int64),
+           ("embed", ChrNf4Dev), ("embed_dense", c_void_p), ("lm_head", ChrNf4Dev)]
+        + [(n, c_void_p) for n in ("final_norm", "cos", "sin", "token", "position", "next_token",
+                                   "valid_len", "finished", "x", "q", "k", "v", "qkv", "attn",
+                                   "down_in", "logits", "attn_ws", "layers", "sync")]
+    )
+
+
+STEP_SYNC_BYTES = 8192
+
 _DEV = POINTER(ChrNf4Dev)
 
 # name -> (restype, argtypes); every symbol include/chr_gpu.h declares.
@@ -99,6 +123,8 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     ),
+    "chr_nf4_decode_step": (c_int, [POINTER(ChrNf4Step), c_void_p]),
+    "chr_nf4_decode_step_status": (c_int, [c_void_p]),
     "chr_nf4_encode_f32": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int32]),
     "chr_nf4_decode_f32": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_int32]),
     "chr_nf4_encode_dev": (

@@ -219,6 +219,71 @@ int chr_nf4_decode_f32(const uint8_t *packed, const uint16_t *scale, int32_t M,
 int chr_nf4_encode_dev(const float *w, int32_t M, int32_t K, uint8_t *packed,
                        uint16_t *scale, int32_t *status, void *stream);
 
+/* ---- Whole greedy step in one persistent launch ---------------------------
+ * The sequence the reference issues as one launch per operation
+ * (gpu/decodev2/step.py:162-187: embed row -> per layer [RMSNorm + q/k/v GEMV,
+ * attention with fused RoPE and KV write, o-proj GEMV + residual, RMSNorm +
+ * SwiGLU GEMV, down-proj GEMV + residual] -> final RMSNorm + lm_head GEMV ->
+ * greedy pick -> commit) runs here as ONE cooperative kernel, one CTA per SM,
+ * with a grid-wide barrier between operations; each CTA has the next
+ * operation's first weight tile in flight while it waits at the barrier.
+ * Results are bit-identical to the per-operation entry points above (same
+ * device code, same work split). Every barrier wait is bounded: when it runs
+ * out the kernel records a code in the sync block and runs to its end without
+ * waiting again (the step's outputs are then undefined).
+ * No counterpart in the reference's C ABI. */
+
+/* One decoder layer. A model with a fused, group-interleaved wqkv matrix
+ * ([n_kv][n_rep + 2][head_dim] rows) passes it as q and leaves k.M = v.M = 0. */
+typedef struct {
+  chr_nf4_dev_t q, k, v, o, gate, up, down;
+  const void *bq, *bk, *bv; /* bf16 biases of q/k/v (of wqkv in bq), or NULL */
+  const void *norm1, *norm2; /* bf16 [hidden] RMSNorm weights */
+  void *k_cache, *v_cache;   /* bf16 [max_seq, n_kv, head_dim] */
+} chr_nf4_step_layer_t;
+
+#define CHR_NF4_STEP_SYNC_BYTES 8192
+
+typedef struct {
+  int32_t n_layers, hidden, intermediate, n_q, n_kv, head_dim, max_seq, vocab;
+  int32_t n_split;     /* attention splits the workspace was sized for (1..64) */
+  int32_t fused_qkv;   /* 1: layers carry wqkv in q, activations go through qkv */
+  int32_t commit;      /* 1: token/position/finished advance; 0: next_token and position only */
+  float rms_eps, attn_scale;
+  int64_t eos;
+  chr_nf4_dev_t embed;       /* packed embedding table, or packed == NULL ... */
+  const void *embed_dense;   /* ... and a bf16 [vocab, hidden] table here */
+  chr_nf4_dev_t lm_head;
+  const void *final_norm;
+  const void *cos, *sin;     /* bf16 [max_seq, head_dim] */
+  void *token, *position, *next_token; /* device int64 */
+  void *valid_len;           /* device int32 */
+  void *finished;            /* device uint8 */
+  void *x, *q, *k, *v, *qkv, *attn, *down_in, *logits; /* bf16 activations */
+  float *attn_ws;            /* n_q * n_split * (head_dim + 2) floats */
+  const chr_nf4_step_layer_t *layers; /* HOST array of n_layers (<= 96) descriptors, read at the call */
+  void *sync;                /* CHR_NF4_STEP_SYNC_BYTES device bytes, zeroed once by the caller */
+} chr_nf4_step_t;
+
+/* Launches one step on `stream`. Returns CHR_* codes; -3 when a shape is outside
+ * what the persistent kernel covers (K beyond 24576, head_dim > 256, hidden not a
+ * multiple of 8, more than 96 layers, a layer whose matrices do not have the
+ * model's dimensions) - use the per-operation entry points then. Capturable; not
+ * re-entrant (call it from one thread at a time). */
+int chr_nf4_decode_step(const chr_nf4_step_t *step, void *stream);
+
+/* Profiling aid: the sync block also records, for the last launch, nanosecond
+ * stamps taken by CTA 0 (64-bit words starting at byte CHR_NF4_STEP_STAMPS_OFFSET:
+ * [0] kernel start, [n] the moment the barrier wait before operation n
+ * completed; operation 1 is layer 0's q/k/v, then attention, o, gate/up, down
+ * per layer, then lm_head and the pick). */
+#define CHR_NF4_STEP_STAMPS_OFFSET 4160
+
+/* Reads (and clears) the status word of a sync block; synchronises the device.
+ * 0 = every barrier completed; 1..999 = the wait before operation n gave up;
+ * 1000 = a token id outside the embedding table was fed (its row reads as zero). */
+int chr_nf4_decode_step_status(void *sync);
+
 #ifdef __cplusplus
 }
 #endif

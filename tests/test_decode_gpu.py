@@ -188,3 +188,102 @@ def test_state_reset_and_registers():
         consume_prompt(state, weights, list(range(17)))
     with pytest.raises(RuntimeError):
         DecodeState.allocate(TINY_LLAMA, torch.zeros(32, 64), device="cpu")
+
+
+def test_token_loop_mma_path_tracks_decode_v2():
+    from gpu.loop import TokenLoop
+
+    model, state, weights = session(MEDIUM_LLAMA, 0)
+    prompt = [1, 3, 5, 7]
+    want = mr.greedy_ids(model, prompt, 8)
+    loop = TokenLoop(state, weights)
+    eager = loop.generate(torch.tensor(prompt), 8).tokens
+    assert loop.capture_graphs() == "tokenloop", loop.graph_error
+    graphed = loop.generate(torch.tensor(prompt), 8)
+    assert graphed.tokens == eager and graphed.graph == "tokenloop"
+    # the MMA path rounds W to bf16, so only the prefill token is pinned to the oracle;
+    # later ids may part at near-ties
+    assert eager[0] == want[0] and len(eager) == len(want)
+    loop.reset()
+    loop.prefill_from(prompt, 0)
+    loop.state.token.copy_(loop.state.next_token)
+    assert loop.step() == eager[1]
+
+
+def test_host_seats_linear_and_embedding(golden):
+    import nf4_ref as o
+    from gpu.chr0.loader import ChrMatrix
+    from gpu.host.embedding import Nf4Embedding, dequant_nf4_rows
+    from gpu.host.linear import CompressedLinear
+
+    rng = np.random.default_rng(0)
+    m, k = 192, 256
+    w = (rng.standard_normal((m, k)) * 0.02).astype(np.float32)
+    p, s = o.quantize(w)
+    mat = ChrMatrix("toy", m, k, k, torch.from_numpy(p).cuda(), torch.from_numpy(s).cuda())
+    seat = CompressedLinear(k, m, bias=True, device="cuda")
+    assert not seat.is_loaded and seat.weight.numel() == 0
+    with pytest.raises(RuntimeError):
+        seat(torch.zeros(1, k, device="cuda", dtype=torch.bfloat16))
+    bias = torch.from_numpy(rng.standard_normal(m).astype(np.float32)).to(torch.bfloat16)
+    seat.attach(mat, bias)
+    x = torch.from_numpy(rng.standard_normal((2, 5, k)).astype(np.float32)).to(torch.bfloat16).cuda()
+    y = seat(x)
+    assert y.shape == (2, 5, m) and y.dtype is torch.bfloat16
+    want = x.float().cpu().numpy().reshape(10, k) @ o.dequantize_bf16(p, s, m, k).T + bias.float().numpy()
+    assert np.abs(y.float().cpu().numpy().reshape(10, m) - want).max() <= 1e-2 * np.abs(want).max()
+    with pytest.raises(ValueError):
+        CompressedLinear(k + 64, m).attach(mat)
+    g = golden("embed_rows.npz")
+    emb = Nf4Embedding(40, 200, device="cuda")
+    emb.attach(ChrMatrix("e", 40, 200, 256, torch.from_numpy(g["packed"]).cuda(),
+                         torch.from_numpy(g["scale"].view(np.float16)).cuda()))
+    ids = torch.from_numpy(g["ids"]).cuda()
+    rows = emb(ids.view(1, -1))
+    assert rows.shape == (1, 5, 200)
+    assert np.array_equal(rows.view(torch.int16).cpu().numpy().view(np.uint16).reshape(5, 200),
+                          g["rows_bf16_bits"])
+    assert torch.equal(dequant_nf4_rows(emb.packed, emb.scale, ids, 200), rows.view(5, 200))
+
+
+@pytest.mark.parametrize("spec,seed,kw", [
+    (TINY_LLAMA, 0, {}),
+    (TINY_INTERNLM, 1, {}),
+    (MEDIUM_LLAMA, 0, {}),
+    (MEDIUM_LLAMA, 0, {"packed_embed": True}),
+])
+def test_persistent_step_is_bit_identical_to_the_launch_chain(spec, seed, kw):
+    _, state, weights = session(spec, seed, **kw)
+    prompt = [1, 3, 5, 7]
+    loop = DecodeV2Loop(state, weights)
+    chain = loop.generate_device_window(prompt, 10)
+    want_logits = state.arena.logits.clone()
+    want_k, want_v = state.kv.k.clone(), state.kv.v.clone()
+    assert loop.enable_fused_step() is None and loop.fused
+    fused = loop.generate_device_window(prompt, 10)
+    assert loop._fused.status() == 0
+    assert fused.tokens == chain.tokens
+    assert torch.equal(state.arena.logits, want_logits)
+    assert torch.equal(state.kv.k, want_k) and torch.equal(state.kv.v, want_v)
+    assert loop.capture_graphs() == "decodev2", loop.graph_error
+    replay = loop.generate_device_window(prompt, 10)
+    assert loop._fused.status() == 0
+    assert replay.tokens == chain.tokens and torch.equal(state.arena.logits, want_logits)
+    # host-visible requests through the same step
+    assert loop.generate(prompt, 6).tokens == chain.tokens[:6]
+    loop.enable_fused_step(False)
+    assert not loop.fused and loop.generate_device_window(prompt, 10).tokens == chain.tokens
+
+
+def test_persistent_step_flags_a_bad_token_id_and_refuses_shards():
+    from gpu.decodev2 import FusedStep, fused_step_supported
+
+    _, state, weights = session(TINY_LLAMA, 0)
+    step = FusedStep(state, weights)
+    state.reset()
+    state.token.fill_(state.spec.vocab + 5)
+    step(state, weights)
+    assert step.status() == 1000 and step.status() == 0
+    with pytest.raises(RuntimeError):
+        step(state, DeviceWeights.from_synth(build(TINY_LLAMA, 0), "cuda", torch.bfloat16))
+    assert fused_step_supported(state, weights) is None
