@@ -33,6 +33,10 @@ for _p in (str(ROOT / "deep-fold_b200"), str(ROOT / "oracle")):
 METRIC = "decode_tok_s_bs1"
 UNIT = "tok/s"
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the timed kernel, from
+# the ncu capture summarised under profiles/ (SwiGLU GEMV, gate/up [M, K]); other
+# shapes scale by their algorithmic bytes (traffic / algorithmic = 1.001 there).
+NCU_TRAFFIC_RATIO = 24004864 / 23979520
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -187,7 +191,10 @@ def run_ours(args, spec) -> None:
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=180))
     from gpu.decodev2 import Comm, shard_weights
 
     # every rank draws the same full model (seeded device RNG) and keeps its shard
@@ -305,8 +312,9 @@ def run_ours(args, spec) -> None:
     if dist is not None:
         dist.barrier()
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        if comm is not None:
+            del step, sweep_graph
+            comm.shutdown(loop)
         return
     if loop.fused:
         launches_per_step = 1  # the whole step is one persistent kernel
@@ -332,7 +340,9 @@ def run_ours(args, spec) -> None:
     gemv_roof = {"kernel": "nf4_gemv_kernel<swiglu> (gate+up, fused RMSNorm)", "bound": "hbm",
                  "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                  "frac": achieved / peak, "bytes_per_launch": per_launch, "us_per_launch": k_us,
-                 "traffic": None}
+                 "traffic": int(round(per_launch * NCU_TRAFFIC_RATIO)),
+                 "traffic_source": "ncu capture of the 3B gate/up launch (24,004,864 B), scaled by "
+                                   "algorithmic bytes for other shapes"}
     if loop.fused:
         # one launch = one token: every packed weight byte and scale is read once
         step_us = dev_ms / args.steps * 1e3
@@ -349,9 +359,10 @@ def run_ours(args, spec) -> None:
     if not args.no_cpu:
         cb = cpu_layer_sample(full_spec)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+    if comm is not None:
+        del step, sweep_graph
+        comm.shutdown(loop)
 
 
 def main() -> None:

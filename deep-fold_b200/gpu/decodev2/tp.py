@@ -41,6 +41,49 @@ class Comm:
             return cls(dist.get_rank(), dist.get_world_size(), None)
         return cls()
 
+    def shutdown(self, *holders, grace_s: float = 20.0) -> None:
+        """Leave the process group at the end of a run.
+
+        ``destroy_process_group`` does not return while a CUDA graph that captured NCCL
+        kernels is alive (seen with torch 2.11 / NCCL 2.28 on two B200s: both ranks sat
+        in it until killed), so the graphs of the given loops are dropped first, the
+        device is drained and the ranks meet at a barrier; the destroy then runs on a
+        helper thread, and a rank whose destroy still has not returned after
+        ``grace_s`` exits the process directly - nothing of its own is in flight by then.
+        """
+        import gc
+        import os
+        import sys
+        import threading
+
+        import torch.distributed as dist
+
+        if not (dist.is_available() and dist.is_initialized()):
+            return
+        for h in holders:
+            if hasattr(h, "_graph"):
+                h._graph = None
+                h.graph_mode = "off"
+        gc.collect()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        done = threading.Event()
+
+        def _destroy() -> None:
+            try:
+                dist.destroy_process_group()
+            finally:
+                done.set()
+
+        threading.Thread(target=_destroy, daemon=True).start()
+        if not done.wait(grace_s):
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
     def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
             import torch.distributed as dist

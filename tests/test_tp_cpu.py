@@ -125,8 +125,16 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str) -> None:
         comm.all_gather_into(gathered, local)
         assert np.abs(gathered.numpy() - deq(full.lm_head) @ h).max() <= 1e-5
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
+
+        class _Loop:  # what shutdown() is handed: something that may hold a captured graph
+            _graph, graph_mode = object(), "decodev2"
+
+        holder = _Loop()
+        comm.shutdown(holder)
+        assert holder._graph is None and not dist.is_initialized()
     finally:
-        dist.destroy_process_group()
+        if dist.is_initialized():
+            dist.destroy_process_group()
 
 
 def test_two_rank_gloo_collectives(tmp_path):

@@ -19,13 +19,19 @@ def _free_port() -> int:
 
 
 def _rank_main(rank: int, world: int, port: int, out_dir: str) -> None:
+    import datetime
+    import faulthandler
+
     import torch.distributed as dist
 
+    # a rank that stops making progress dumps its stack and exits instead of holding the box
+    faulthandler.dump_traceback_later(240, exit=True)
     from gpu.decodev2 import (MEDIUM_LLAMA, Comm, DecodeV2Loop, DeviceWeights, build, shard_weights)
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
     try:
         model = build(MEDIUM_LLAMA, 0)
         full = DeviceWeights.from_synth(model, f"cuda:{rank}")
@@ -41,8 +47,11 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str) -> None:
         dist.barrier()
         with open(os.path.join(out_dir, f"r{rank}"), "w") as f:
             f.write(repr((want, eager, mode, loop.graph_error, graphed, chunked)))
+            f.flush()
+            os.fsync(f.fileno())
+        loop.state.comm.shutdown(loop)
     finally:
-        dist.destroy_process_group()
+        faulthandler.cancel_dump_traceback_later()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
