@@ -13,6 +13,7 @@
 namespace chr {
 
 constexpr int kAttnWarps = 8;
+constexpr int kAttnAhead = 4;       // cache rows in flight per warp
 constexpr int kAttnMaxSplit = 16;  // splits actually used: min(n_split, 16)
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr float kNegInit = -1.0e30f;
@@ -153,10 +154,10 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, AttnSmem<P, H> &sm,
     for (int e = 0; e < 2 * P; ++e) acc[h][e] = 0.f;
   }
 
-  // Token loop, one token ahead: the next row's K/V are in flight while this one
-  // is scored. Row t of this warp: split + warp*n_split + i*4*n_split.
+  // Token loop with kAttnAhead rows in flight per warp: a row's K/V are requested
+  // that many rows before they are scored. Row i of this warp: split + warp*n_split
+  // + i*kAttnWarps*n_split.
   const int t_step = kAttnWarps * n_split;
-  uint32_t kb[P], vb[P], kb_n[P], vb_n[P];
   auto fetch = [&](int t, uint32_t (&kk)[P], uint32_t (&vv)[P]) {
     const size_t row = (static_cast<size_t>(t) * n_kv + kvh) * hd;
 #pragma unroll
@@ -167,10 +168,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, AttnSmem<P, H> &sm,
       vv[p] = live ? __ldg(reinterpret_cast<const uint32_t *>(a.v_cache + row + d)) : 0u;
     }
   };
-  int t = split + warp * n_split;
-  fetch(t, kb, vb);
-  for (; t < vl; t += t_step) {
-    fetch(t + t_step, kb_n, vb_n);
+  auto score = [&](int t, const uint32_t (&kb)[P], const uint32_t (&vb)[P]) {
     float kk[2 * P], vv[2 * P];
     const bool cur = fuse_kv && t == pos;
 #pragma unroll
@@ -212,10 +210,17 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, AttnSmem<P, H> &sm,
       for (int e = 0; e < 2 * P; ++e) acc[h][e] = acc[h][e] * alpha + ex * vv[e];
       m[h] = m2;
     }
+  };
+  uint32_t kq[kAttnAhead][P], vq[kAttnAhead][P];
+  int t = split + warp * n_split;
 #pragma unroll
-    for (int p = 0; p < P; ++p) {
-      kb[p] = kb_n[p];
-      vb[p] = vb_n[p];
+  for (int d = 0; d < kAttnAhead; ++d) fetch(t + d * t_step, kq[d], vq[d]);
+  for (; t < vl; t += kAttnAhead * t_step) {
+#pragma unroll
+    for (int d = 0; d < kAttnAhead; ++d) {
+      const int tt = t + d * t_step;
+      if (tt < vl) score(tt, kq[d], vq[d]);
+      fetch(tt + kAttnAhead * t_step, kq[d], vq[d]);
     }
   }
 

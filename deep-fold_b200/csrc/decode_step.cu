@@ -36,14 +36,19 @@ namespace {
 constexpr int kStepWarps = CHR_STEP_WARPS;
 constexpr int kStepThreads = kStepWarps * 32;
 static_assert(kStepWarps <= kMaxWarps && kStepThreads >= kAttnThreads, "step CTA");
-constexpr int kStepHeadBytes = kPartBytes;  // GemvArgs + slice partials
-constexpr int kStepAttnBytes = kXsBytes;    // attention scratch and the GEMVs' staged x share it
-constexpr int kStepSmemBytes = kStepHeadBytes + kStepAttnBytes + 2 * kTabBytes;
+constexpr int kStepHeadBytes = kPartBytes;  // wait flag + slice partials
+constexpr int kStepAttnBytes = 40960;       // attention scratch; the GEMVs' staged x shares it
 constexpr unsigned int kBarrierPolls = 1u << 21;
 
 static_assert(sizeof(AttnSmem<4, 4>) <= kStepAttnBytes, "attention scratch");
 static_assert(sizeof(AttnSmem<2, 8>) <= kStepAttnBytes, "attention scratch");
 static_assert(64 + 2 * kMaxWarps * 8 * sizeof(float) <= kStepHeadBytes, "head region");
+
+// Shared memory of the step kernel for a model whose longest GEMV input is max_k.
+int step_smem_bytes(int max_k) {
+  const int xs = ((max_k + 7) / 8) * 16;
+  return table_smem_request(xs > kStepAttnBytes ? xs : kStepAttnBytes);
+}
 
 // Layout of the caller's sync block (32-bit words).
 constexpr int kSyncBar = 0;      // arrivals of the running launch
@@ -291,8 +296,13 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const Step
   float *part = reinterpret_cast<float *>(smem + 64);
   void *attn_scratch = smem + kStepHeadBytes;
   __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(smem + kStepHeadBytes);
-  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-  const uint32_t tab_base = (smem_base + kStepHeadBytes + kStepAttnBytes + 0xFFFFu) & ~0xFFFFu;
+  const uint32_t tab_base = pair_table_base(smem);
+  if (tab_base == 0u) {  // mis-sized launch (the entry point never produces one)
+    if (blockIdx.x == 0 && tid == 0) {
+      atomicCAS(reinterpret_cast<int *>(sync_words + kSyncStatus), 0, 3000);
+    }
+    return;
+  }
   const uint32_t tab_lane = tab_base + static_cast<uint32_t>(tid & 31) * 8u;
 
   GridBarrier gb{sync_words + kSyncBar, reinterpret_cast<int *>(sync_words + kSyncStatus), flag,
@@ -414,20 +424,22 @@ GemvArgs gemv_args(const GemvShape &sh, int n_rows, int K, int K_pad, const void
 }
 
 // CTAs of the step kernel that fit the current device at once (one per SM when it fits).
-int step_grid() {
+int step_grid(int smem_bytes) {
+  static int attr_bytes[kMaxStepDevices] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxStepDevices) return 0;
-  if (g_step_grid[dev] > 0) return g_step_grid[dev];
+  if (attr_bytes[dev] >= smem_bytes && g_step_grid[dev] > 0) return g_step_grid[dev];
   if (cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kStepSmemBytes) != cudaSuccess) {
+                           smem_bytes) != cudaSuccess) {
     return 0;
   }
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, kStepThreads,
-                                                    kStepSmemBytes) != cudaSuccess ||
+                                                    smem_bytes) != cudaSuccess ||
       per_sm < 1) {
     return 0;
   }
+  attr_bytes[dev] = smem_bytes;
   g_step_grid[dev] = sm_count();
   return g_step_grid[dev];
 }
@@ -484,7 +496,12 @@ extern "C" int chr_nf4_decode_step(const chr_nf4_step_t *step, void *stream) {
       !aligned(s.sync, 8) || !aligned(s.lm_head.packed, 16)) {
     return kAlign;
   }
-  const int grid = step_grid();
+  const int q_dim_all = s.n_q * s.head_dim;
+  const int max_k = s.intermediate > s.hidden ? (s.intermediate > q_dim_all ? s.intermediate : q_dim_all)
+                                              : (s.hidden > q_dim_all ? s.hidden : q_dim_all);
+  const int smem_bytes = step_smem_bytes(max_k);
+  if (smem_bytes == 0) return kDims;
+  const int grid = step_grid(smem_bytes);
   if (grid < 1) return kLaunch;
 
   if (s.n_layers > kMaxStepLayers) return kDims;
@@ -601,7 +618,7 @@ extern "C" int chr_nf4_decode_step(const chr_nf4_step_t *step, void *stream) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
   cfg.blockDim = dim3(kStepThreads);
-  cfg.dynamicSmemBytes = kStepSmemBytes;
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;

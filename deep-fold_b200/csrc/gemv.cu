@@ -16,6 +16,7 @@ nf4_gemv_kernel(const GemvArgs a) {
   // in flight inside gemv_run before the table is built and x is read.
   pdl_trigger();
   const uint32_t tab_base = pair_table_base(smem);
+  if (tab_base == 0u) return;  // mis-sized launch: the host entry points never produce one
   const uint32_t tab_lane = tab_base + static_cast<uint32_t>(threadIdx.x & 31) * 8u;
   gemv_run<R, C, MODE>(a, reinterpret_cast<float *>(smem),
                        reinterpret_cast<__nv_bfloat16 *>(smem + kPartBytes), tab_lane, blockIdx.x,
@@ -27,12 +28,19 @@ nf4_gemv_kernel(const GemvArgs a) {
                        });
 }
 
+__global__ void smem_offset_probe(int *out) {
+  extern __shared__ __align__(16) unsigned char probe_smem[];
+  if (threadIdx.x == 0) *out = static_cast<int>(__cvta_generic_to_shared(probe_smem));
+}
+
 template <int MODE>
 int launch(const GemvArgs &proto, cudaStream_t st) {
   constexpr bool swiglu = MODE == 1;
   GemvArgs a = proto;
   const GemvShape sh = pick_gemv_shape(a.n_rows, a.K_pad, swiglu, sm_count());
   if (sh.R == 0) return kDims;  // K beyond 16 slices of 2048 is not supported by this path
+  const int smem_bytes = table_smem_request(((a.K + 7) / 8) * 16);
+  if (smem_bytes == 0) return kDims;  // x does not fit in front of the table
   a.S = sh.S;
   a.G = sh.G;
   a.n_tiles = sh.n_tiles;
@@ -41,16 +49,16 @@ int launch(const GemvArgs &proto, cudaStream_t st) {
 
 #define CHR_LAUNCH(RR, CC)                                                                   \
   do {                                                                                       \
-    static bool attr_done = false;                                                           \
-    if (!attr_done) {                                                                        \
+    static int attr_bytes = 0;                                                               \
+    if (attr_bytes < smem_bytes) {                                                           \
       if (cudaFuncSetAttribute(nf4_gemv_kernel<RR, CC, MODE>,                                \
                                cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
-                               kSmemBytes) != cudaSuccess) {                                 \
+                               smem_bytes) != cudaSuccess) {                                 \
         return kLaunch;                                                                      \
       }                                                                                      \
-      attr_done = true;                                                                      \
+      attr_bytes = smem_bytes;                                                               \
     }                                                                                        \
-    if (launch_chain(nf4_gemv_kernel<RR, CC, MODE>, grid, block, kSmemBytes, st, a) !=       \
+    if (launch_chain(nf4_gemv_kernel<RR, CC, MODE>, grid, block, smem_bytes, st, a) !=       \
         cudaSuccess) {                                                                       \
       return kLaunch;                                                                        \
     }                                                                                        \
@@ -76,6 +84,25 @@ int launch(const GemvArgs &proto, cudaStream_t st) {
 }
 
 }  // namespace
+
+int smem_window_offset() {
+  static int cached[64];
+  static bool have[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (have[dev]) return cached[dev];
+  int *d = nullptr;
+  int v = -1;
+  if (cudaMalloc(&d, sizeof(int)) != cudaSuccess) return -1;
+  smem_offset_probe<<<1, 32, 1024>>>(d);
+  const bool ok = cudaMemcpy(&v, d, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess;
+  cudaFree(d);
+  if (!ok || v < 0 || v > 16384) return -1;
+  cached[dev] = v;
+  have[dev] = true;
+  return v;
+}
+
 }  // namespace chr
 
 using namespace chr;

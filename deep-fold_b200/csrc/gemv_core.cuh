@@ -26,6 +26,8 @@
 // order differs from the reference's, which stays inside its 1e-2 tolerance.
 #pragma once
 
+#include <cstdlib>
+
 #include "nf4_common.cuh"
 
 namespace chr {
@@ -36,10 +38,34 @@ constexpr int kChunk = 1024;        // k per warp-wide 16-byte load
 #endif
 constexpr int kMaxWarps = CHR_GEMV_MAX_WARPS;
 constexpr int kTabBytes = 65536;    // 256 byte values x 32 lanes x float2
-constexpr int kPartBytes = 16384;   // slice partials (and the step kernel's operation record)
-constexpr int kXsBytes = 65536;     // staged activation vector: K <= 32768 bf16
-constexpr int kHeadBytes = kPartBytes + kXsBytes;
-constexpr int kSmemBytes = kHeadBytes + 2 * kTabBytes;  // room to place the table on a 64 KiB boundary
+// Dynamic shared memory of the kernels that use the pair table:
+//   [ slice partials kPartBytes | head: staged x (or attention scratch) | pad | table 64 KiB ]
+// The table is the LAST 64 KiB of the allocation and must start on a 64 KiB
+// boundary of the shared window. Dynamic shared memory starts a few hundred bytes
+// into the window (the driver reserves 1 KiB; these kernels declare no static
+// shared memory), so the host asks for exactly as much as puts the end of the
+// allocation on a boundary: 127 KiB when partials + head fit in 63 KiB. Keeping the
+// footprint there matters: the unified L1 holds the weight loads in flight, and at
+// 208 KiB of shared memory the 16 warps' 64 KiB of outstanding loads no longer fit
+// in what is left of it (measured: lm_head 49 -> 60 us, gate+up 10.7 -> 12.2 us).
+constexpr int kPartBytes = 2048;
+constexpr int kWindowBytes = 65536;
+
+// Offset of dynamic shared memory inside the shared window for kernels without
+// static shared memory, measured once per device by a probe launch (not capturable:
+// the first launch on a device must happen outside stream capture).
+int smem_window_offset();
+
+// Bytes to request so that the table (last 64 KiB) is aligned; 0 when partials +
+// head_bytes cannot be placed in front of it within the 227 KiB a CTA may have.
+inline int table_smem_request(int head_bytes) {
+  const int off = smem_window_offset();
+  if (off < 0) return 0;
+  const int front = off + kPartBytes + head_bytes;
+  const int table_at = (front + kWindowBytes - 1) / kWindowBytes * kWindowBytes;
+  const int request = table_at - off + kTabBytes;
+  return request <= 232448 ? request : 0;
+}
 
 struct GemvArgs {
   const uint8_t *packed[3];
@@ -104,9 +130,14 @@ __device__ __forceinline__ void build_pair_table(uint32_t tab_base, int tid, int
   }
 }
 
+// Shared address of the table: the last 64 KiB of the dynamic allocation. Returns 0
+// (never a valid table address) if the host's sizing did not land it on a boundary.
 __device__ __forceinline__ uint32_t pair_table_base(const void *smem) {
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-  return (smem_base + kHeadBytes + 0xFFFFu) & ~0xFFFFu;
+  uint32_t dyn;
+  asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+  const uint32_t tab = smem_base + dyn - kTabBytes;
+  return (dyn >= kTabBytes && (tab & 0xFFFFu) == 0u) ? tab : 0u;
 }
 
 // Sum R per-lane values over the warp with half the shuffles of R butterflies.
@@ -238,7 +269,7 @@ __device__ __forceinline__ void gemv_run(const GemvArgs &a, float *part, __nv_bf
   bool chunk_live[C];
 #pragma unroll
   for (int j = 0; j < C; ++j) {
-    chunk_live[j] = live_warp && (s * C + j) * kChunk + lane * 32 < a.K_pad;
+    chunk_live[j] = (s * C + j) * kChunk + lane * 32 < a.K_pad;
   }
   // this lane's byte / scale offset inside any row (chunk j adds j*512 bytes, j*16 scales)
   const size_t lane_pk = static_cast<size_t>(s) * C * (kChunk / 2) + static_cast<size_t>(lane) * 16;
@@ -289,7 +320,32 @@ __device__ __forceinline__ void gemv_run(const GemvArgs &a, float *part, __nv_bf
   // in flight before waiting for it.
   int tile = first_tile;
   const bool any = tile < a.n_tiles;
-  if (any) issue(tile, cur, cur_s);
+  if (any && live_warp) issue(tile, cur, cur_s);
+
+  // The RMSNorm weights are constants too: fetch the lane's slice before waiting, so
+  // that after the wait only x itself is on the critical path.
+  uint4 wv[C][4];
+#pragma unroll
+  for (int j = 0; j < C; ++j) {
+    const int k0 = (s * C + j) * kChunk + lane * 32;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int k = k0 + q * 8;
+      wv[j][q] = make_uint4(0u, 0u, 0u, 0u);
+      if (any && live_warp && a.rms_w != nullptr && k < a.K) {
+        if (k + 8 <= a.K) {
+          wv[j][q] = __ldg(reinterpret_cast<const uint4 *>(a.rms_w + k));
+        } else {
+          __nv_bfloat16 tw[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            tw[e] = k + e < a.K ? a.rms_w[k + e] : __float2bfloat16(0.f);
+          }
+          wv[j][q] = *reinterpret_cast<const uint4 *>(tw);
+        }
+      }
+    }
+  }
   wait();
   if (!any) return;
 
@@ -319,8 +375,11 @@ __device__ __forceinline__ void gemv_run(const GemvArgs &a, float *part, __nv_bf
   // copy in the order of warp_sumsq_bf16 (lane l owns the 8-element groups l, l+32,
   // ...; zero padding adds nothing), so every kernel that needs the scale gets the
   // same bits.
+  // Warps beyond S*G have nothing more to do: the barriers below count S*G warps.
+  if (!live_warp) return;
+  const int live_threads = a.S * a.G * 32;
   float inv = 1.f;
-  if (a.rms_w != nullptr && live_warp) {
+  if (a.rms_w != nullptr) {
     float acc = 0.f;
 #pragma unroll 4
     for (int g8 = lane; g8 < n8; g8 += 32) {
@@ -346,24 +405,9 @@ __device__ __forceinline__ void gemv_run(const GemvArgs &a, float *part, __nv_bf
     for (int q = 0; q < 4; ++q) {
       const int k = k0 + q * 8;
       uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-      uint4 wv = make_uint4(0u, 0u, 0u, 0u);
-      if (live_warp && k < a.K) {
-        xv = xs4[k >> 3];
-        if (a.rms_w != nullptr) {
-          if (k + 8 <= a.K) {
-            wv = __ldg(reinterpret_cast<const uint4 *>(a.rms_w + k));
-          } else {
-            __nv_bfloat16 tw[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              tw[e] = k + e < a.K ? a.rms_w[k + e] : __float2bfloat16(0.f);
-            }
-            wv = *reinterpret_cast<const uint4 *>(tw);
-          }
-        }
-      }
+      if (k < a.K) xv = xs4[k >> 3];
       const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      const uint32_t ww[4] = {wv[j][q].x, wv[j][q].y, wv[j][q].z, wv[j][q].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float lo = bf16_lo(xw[e]);
@@ -400,26 +444,23 @@ __device__ __forceinline__ void gemv_run(const GemvArgs &a, float *part, __nv_bf
   int buf = 0;
   auto process = [&](int tile, const uint4 (&pk)[RW][C], const uint16_t (&sc)[RW][C]) {
     constexpr int lanes_per = 32 / RW;
-    float tot = 0.f;
-    const int my = reduced_row_of_lane<RW>(lane);  // weight-row index this lane holds
-    if (live_warp) {
-      float sum[RW];
+    float sum[RW];
 #pragma unroll
-      for (int i = 0; i < RW; ++i) {
-        sum[i] = 0.f;
+    for (int i = 0; i < RW; ++i) {
+      sum[i] = 0.f;
 #pragma unroll
-        for (int j = 0; j < C; ++j) {
-          const float d = dot32(pk[i][j], xr[j], tab_lane);
-          sum[i] = fmaf(half_bits_to_float(sc[i][j]), d, sum[i]);
-        }
+      for (int j = 0; j < C; ++j) {
+        const float d = dot32(pk[i][j], xr[j], tab_lane);
+        sum[i] = fmaf(half_bits_to_float(sc[i][j]), d, sum[i]);
       }
-      tot = warp_reduce_rows<RW>(sum, lane);
     }
+    const float tot = warp_reduce_rows<RW>(sum, lane);
+    const int my = reduced_row_of_lane<RW>(lane);  // weight-row index this lane holds
 
     if (a.S > 1) {
       float *pb = part + buf * (kMaxWarps * 8);
-      if (live_warp && (lane & (lanes_per - 1)) == 0) pb[s * (a.G * RW) + g * RW + my] = tot;
-      __syncthreads();
+      if ((lane & (lanes_per - 1)) == 0) pb[s * (a.G * RW) + g * RW + my] = tot;
+      asm volatile("bar.sync 2, %0;" ::"r"(live_threads) : "memory");
       if (tid < rt) {
         const int unit = tile * rt + tid;
         if constexpr (MODE == 1) {
@@ -438,7 +479,7 @@ __device__ __forceinline__ void gemv_run(const GemvArgs &a, float *part, __nv_bf
         }
       }
       buf ^= 1;
-    } else if (live_warp) {
+    } else {
       if constexpr (MODE == 1) {
         // lanes of weight-row 2u hold gate, of 2u+1 hold up: fetch the partner.
         const float other = __shfl_xor_sync(0xffffffffu, tot, lanes_per);
@@ -473,8 +514,18 @@ struct GemvShape {
 
 // K slices of C*1024 per warp, up to kMaxWarps warps per CTA. Rows per warp (R) and
 // row groups per CTA (G) minimise the number of passes the busiest CTA makes over
-// `ctas` CTAs, with a small per-tile charge so that long matrices amortise the
-// reduction. R == 0 in the result: K is beyond kMaxWarps slices of 2048.
+// `ctas` CTAs, with a per-tile charge (one row's worth by default, CHR_GEMV_TILE_COST
+// overrides it) so that fewer, fatter passes win when a pass is short. R == 0 in the result: K is beyond kMaxWarps slices of 2048.
+inline float gemv_tile_cost() {
+  static float cached = -1.f;
+  if (cached < 0.f) {
+    const char *env = std::getenv("CHR_GEMV_TILE_COST");
+    const float v = env != nullptr ? static_cast<float>(std::atof(env)) : 0.f;
+    cached = (env != nullptr && v >= 0.f && v <= 16.f) ? v : 1.0f;
+  }
+  return cached;
+}
+
 inline GemvShape pick_gemv_shape(int n_rows, int K_pad, bool swiglu, int ctas,
                                  int max_warps = kMaxWarps) {
   GemvShape best{0, 0, 0, 0, 0, 0};
@@ -488,7 +539,7 @@ inline GemvShape pick_gemv_shape(int n_rows, int K_pad, bool swiglu, int ctas,
     for (int R = rmax; R >= 1; R >>= 1) {
       const int tiles = (n_rows + G * R - 1) / (G * R);
       const int passes = (tiles + ctas - 1) / ctas;
-      const float cost = static_cast<float>(passes) * (static_cast<float>(R) + 0.25f);
+      const float cost = static_cast<float>(passes) * (static_cast<float>(R) + gemv_tile_cost());
       if (best.R == 0 || cost < best_cost) {
         best_cost = cost;
         best = GemvShape{R, C, S, G, tiles, tiles < ctas ? tiles : ctas};
