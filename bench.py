@@ -36,7 +36,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the timed kernel, from
 # the ncu capture summarised under profiles/ (SwiGLU GEMV, gate/up [M, K]); other
 # shapes scale by their algorithmic bytes (traffic / algorithmic = 1.001 there).
-NCU_TRAFFIC_RATIO = 24004864 / 23979520
+NCU_TRAFFIC_RATIO = 24002560 / 23979520
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -341,7 +341,7 @@ def run_ours(args, spec) -> None:
                  "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                  "frac": achieved / peak, "bytes_per_launch": per_launch, "us_per_launch": k_us,
                  "traffic": int(round(per_launch * NCU_TRAFFIC_RATIO)),
-                 "traffic_source": "ncu capture of the 3B gate/up launch (24,004,864 B), scaled by "
+                 "traffic_source": "ncu capture of the 3B gate/up launch (24,002,560 B), scaled by "
                                    "algorithmic bytes for other shapes"}
     if loop.fused:
         # one launch = one token: every packed weight byte and scale is read once
