@@ -205,6 +205,9 @@ def run_ours(args, spec) -> None:
         torch.cuda.empty_cache()
     spec = weights.spec
     loop = DecodeV2Loop.from_weights(weights, comm=comm)
+    exchange = "none"
+    if comm is not None:
+        exchange = "nccl" if args.nccl else f"peer memory ({loop.state.enable_peer_exchange()})"
     gen = torch.Generator().manual_seed(2)
     prompt = torch.randint(0, spec.vocab, (args.prompt,), generator=gen).tolist()
     loop.warmup(prompt=8, tokens=4)
@@ -356,6 +359,7 @@ def run_ours(args, spec) -> None:
     else:
         line["roofline"] = gemv_roof
         line["step_mode"] = f"launch chain ({fused_why})"
+    line["config"]["row_split_exchange"] = exchange
     if not args.no_cpu:
         cb = cpu_layer_sample(full_spec)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -374,6 +378,9 @@ def main() -> None:
     ap.add_argument("--model", default="qwen2.5-3b-arch")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--nccl", action="store_true",
+                    help="N > 1: sum the row-split partials with NCCL all-reduce launches instead of "
+                         "inside the GEMV launch over peer memory")
     ap.add_argument("--fused", action="store_true",
                     help="run the step as one persistent kernel instead of the graph of one launch "
                          "per operation (same bits; slower on the 3B shapes as measured)")

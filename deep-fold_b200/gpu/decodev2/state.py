@@ -135,6 +135,20 @@ class DecodeState:
     embed: "torch.Tensor | PackedEmbed"
     eos_id: torch.Tensor
     comm: object = None          # tp.Comm; None = single GPU
+    peers: object = None         # tp.PeerExchange: row-split sums over peer memory instead of NCCL
+
+    def enable_peer_exchange(self, on: bool = True) -> str | None:
+        """Sum the row-split partials inside the GEMV launch, over NVLink peer memory
+        (collective: call it on every rank at the same point). Returns how the buffers
+        were mapped, or ``None`` when switched off / single GPU."""
+        if not on or self.comm is None or self.comm.world < 2:
+            self.peers = None
+            return None
+        if self.peers is None:
+            from .tp import PeerExchange
+
+            self.peers = PeerExchange(self.comm, self.spec.hidden, self.device)
+        return self.peers.how
 
     @classmethod
     def allocate(cls, spec: ArchSpec, embed, *, device=None, dtype: torch.dtype = torch.bfloat16,

@@ -14,8 +14,8 @@ from __future__ import annotations
 
 import torch
 
-from gpu.nf4 import (ATTN_SPLIT, nf4_attn, nf4_gemv, nf4_gemv_f32, nf4_pick_commit, nf4_qkv,
-                     nf4_rms, nf4_swiglu)
+from gpu.nf4 import (ATTN_SPLIT, nf4_attn, nf4_gemv, nf4_gemv_allreduce, nf4_gemv_f32,
+                     nf4_pick_commit, nf4_qkv, nf4_rms, nf4_swiglu)
 
 from .embed import PackedEmbed
 from .linear import DeviceLayer, DeviceLinear, DeviceWeights
@@ -74,12 +74,18 @@ def _qkv(state: DecodeState, layer: DeviceLayer) -> None:
 
 def _accumulate(state: DecodeState, mat: DeviceLinear, src: torch.Tensor, dest: torch.Tensor) -> None:
     """``dest += W @ src``. Single GPU: one launch, residual fused into the GEMV
-    epilogue. Row-split shard: FP32 partial -> sum all-reduce -> one rounded add."""
+    epilogue. Row-split shard: FP32 partial -> sum over ranks -> one rounded add, either as
+    one launch that exchanges the partials over peer memory (``state.peers``) or as GEMV +
+    NCCL all-reduce + add."""
     if state.spec.tp == 1:
         nf4_gemv(mat.packed, mat.scale, src.reshape(mat.K), mat.M, mat.K, mat.K_pad,
                  dest.view(-1), dest.view(-1))
         if mat.bias is not None:
             dest.view(-1).add_(mat.bias.to(dtype=dest.dtype))
+        return
+    if state.peers is not None:  # partial, exchange over peer memory and sum in one launch
+        nf4_gemv_allreduce(mat.packed, mat.scale, src.reshape(mat.K), mat.M, mat.K, mat.K_pad,
+                           dest.view(-1), state.peers.for_matrix(mat), mat.bias)
         return
     part = state.arena.partial
     nf4_gemv_f32(mat.packed, mat.scale, src.reshape(mat.K), mat.M, mat.K, mat.K_pad, part, mat.bias)

@@ -22,7 +22,8 @@ import torch
 from .arch import ArchSpec, group_range, shard_spec
 from .linear import DeviceLayer, DeviceLinear, DeviceWeights
 
-__all__ = ["Comm", "shard_linear_cols", "shard_linear_rows", "shard_weights", "kv_head_rows"]
+__all__ = ["Comm", "PeerExchange", "shard_linear_cols", "shard_linear_rows", "shard_weights",
+           "kv_head_rows"]
 
 
 @dataclass
@@ -100,6 +101,97 @@ class Comm:
         else:
             out.copy_(part.reshape(out.shape))
         return out
+
+
+class PeerExchange:
+    """Buffers of the fused row-split GEMV + all-reduce (``chr_nf4_gemv_allreduce``).
+
+    Every rank allocates a receive buffer (two epochs x one slot per source rank x
+    ``max_rows`` floats) and a block of flag words in memory that all ranks of the box
+    can address, exchanges the mappings once, and keeps the ``chr_nf4_peers_t`` the
+    kernel takes. Mapping goes through torch's symmetric memory (NVLink peer access,
+    multicast left off); when that is unavailable, through CUDA IPC handles of ordinary
+    allocations. Collective: every rank of ``comm`` must construct it at the same point.
+    """
+
+    def __init__(self, comm: Comm, max_rows: int, device) -> None:
+        import os
+
+        import torch.distributed as dist
+
+        from gpu.nf4._lib import AR_MAX_CTAS, AR_MAX_RANKS, ChrNf4Peers
+
+        if comm.world < 2 or comm.world > AR_MAX_RANKS:
+            raise ValueError(f"peer exchange needs 2..{AR_MAX_RANKS} ranks, got {comm.world}")
+        self.comm, self.max_rows = comm, int(max_rows)
+        self._per_shape: dict = {}
+        dev = torch.device(device)
+        n_recv = 2 * comm.world * self.max_rows              # float32
+        n_flags = comm.world * AR_MAX_CTAS                   # uint32, kept as int32
+        n_words = n_recv + n_flags
+        self.how = "symmetric_memory"
+        try:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+
+            buf = symm.empty(n_words, dtype=torch.float32, device=dev)
+            buf.zero_()
+            hdl = symm.rendezvous(buf, dist.group.WORLD if comm.group is None else comm.group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            self._keep = (buf, hdl)
+        except Exception as exc:  # noqa: BLE001 - fall back to IPC handles
+            self.how = f"cuda_ipc ({type(exc).__name__})"
+            buf = torch.zeros(n_words, dtype=torch.float32, device=dev)
+            handle = buf.untyped_storage()._share_cuda_()
+            gathered: list = [None] * comm.world
+            dist.all_gather_object(gathered, handle, group=comm.group)
+            opened, ptrs = [], []
+            for r, h in enumerate(gathered):
+                if r == comm.rank:
+                    ptrs.append(buf.data_ptr())
+                    continue
+                st = torch.UntypedStorage._new_shared_cuda(*h)
+                opened.append(st)
+                ptrs.append(st.data_ptr())
+            self._keep = (buf, opened)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=comm.group)
+        self.local = buf
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.status = torch.zeros((), dtype=torch.int32, device=dev)
+        peers = ChrNf4Peers()
+        peers.rank, peers.world = comm.rank, comm.world
+        for r, base in enumerate(ptrs):
+            peers.recv[r] = base
+            peers.flags[r] = base + 4 * n_recv
+        peers.epoch, peers.status = self.epoch.data_ptr(), self.status.data_ptr()
+        self.peers = peers
+
+    def for_matrix(self, mat: DeviceLinear):
+        """The ``chr_nf4_peers_t`` to pass for this row-split matrix: carries the largest
+        ``K_pad`` any rank holds for it, so that all ranks tile its rows alike. The first
+        call per shape is a collective (max over ranks) and must happen outside capture."""
+        key = (int(mat.M), int(mat.K_pad))
+        got = self._per_shape.get(key)
+        if got is None:
+            import ctypes
+
+            import torch.distributed as dist
+
+            widest = torch.tensor([int(mat.K_pad)], dtype=torch.int64, device=self.local.device)
+            dist.all_reduce(widest, op=dist.ReduceOp.MAX, group=self.comm.group)
+            got = type(self.peers)()
+            ctypes.memmove(ctypes.byref(got), ctypes.byref(self.peers), ctypes.sizeof(got))
+            got.shape_k_pad = int(widest.item())
+            self._per_shape[key] = got
+        return got
+
+    def timed_out(self) -> bool:
+        """True when some wait for a peer ran out of polls since the last call (host read)."""
+        hit = bool(self.status.item())
+        if hit:
+            self.status.zero_()
+        return hit
 
 
 def _rows(mat: DeviceLinear, lo: int, hi: int) -> DeviceLinear:

@@ -31,6 +31,7 @@ __all__ = [
     "nf4_gemm_rows",
     "nf4_gemm_status",
     "nf4_gemv",
+    "nf4_gemv_allreduce",
     "nf4_gemv_f32",
     "nf4_pick_commit",
     "nf4_plan",
@@ -307,6 +308,34 @@ def nf4_gemv_f32(
     _lib.check(rc, "chr_nf4_gemv_f32")
     del keep
     return out
+
+
+def nf4_gemv_allreduce(
+    packed: torch.Tensor,
+    scale: torch.Tensor,
+    x: torch.Tensor,
+    M: int,  # noqa: N803
+    K: int,  # noqa: N803
+    K_pad: int,  # noqa: N803
+    y: torch.Tensor,
+    peers,
+    add: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Row-split shard: ``y += sum over ranks of (W_shard @ x_shard)`` in one launch per rank.
+
+    ``peers`` is a ``ChrNf4Peers`` whose buffers are mapped on every rank (see
+    ``gpu.decodev2.tp.PeerExchange``); ``y`` is the bf16 residual, updated in place and
+    identical on all ranks afterwards; ``add`` an optional bf16 bias (pass it on one rank)."""
+    dev, keep = _matrix(packed, scale, M, K, K_pad)
+    xk = _kvec(x, int(K))
+    _out_vec(y, int(M))
+    add_t = _opt_bf16(add, int(M), "add", exact=False)
+    rc = _lib.load().chr_nf4_gemv_allreduce(
+        ctypes.byref(dev), _ptr(xk), _ptr(y), ctypes.byref(peers), _ptr(add_t), _stream()
+    )
+    _lib.check(rc, "chr_nf4_gemv_allreduce")
+    del keep
+    return y
 
 
 def nf4_qkv(

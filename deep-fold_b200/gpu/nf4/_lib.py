@@ -69,6 +69,17 @@ class ChrNf4Step(Structure):
 
 
 STEP_SYNC_BYTES = 8192
+AR_MAX_RANKS = 8
+AR_MAX_CTAS = 256
+
+
+class ChrNf4Peers(Structure):
+    """Mirror of ``chr_nf4_peers_t``."""
+
+    _fields_ = [("rank", c_int32), ("world", c_int32), ("shape_k_pad", c_int32),
+                ("reserved", c_int32), ("recv", c_void_p * AR_MAX_RANKS),
+                ("flags", c_void_p * AR_MAX_RANKS), ("epoch", c_void_p), ("status", c_void_p)]
+
 
 _DEV = POINTER(ChrNf4Dev)
 
@@ -84,6 +95,9 @@ SIGNATURES = {
     "chr_nf4_set_tuning": (None, [c_int32, c_int32, c_int32]),
     "chr_nf4_gemv": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
     "chr_nf4_gemv_f32": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
+    "chr_nf4_gemv_allreduce": (
+        c_int, [_DEV, c_void_p, c_void_p, POINTER(ChrNf4Peers), c_void_p, c_void_p]
+    ),
     "chr_nf4_gemv_qkv": (
         c_int,
         [_DEV, _DEV, _DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

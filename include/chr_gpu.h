@@ -138,6 +138,42 @@ const char *chr_nf4_version(void);
 int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y, void *stream,
                      const void *add, const void *rms_w, float rms_eps);
 
+/* Row-split linear of a tensor-parallel shard with the exchange fused in: ONE
+ * launch per rank computes this rank's FP32 partial W_shard . x_shard, pushes its
+ * rows into every peer's receive buffer over NVLink (plain peer stores), raises a
+ * per-CTA flag on each peer, waits (bounded) for the peers' flags, sums the
+ * partials in rank order, adds the residual and rounds once:
+ *   y[m] = bf16( f32(y[m]) + sum_r partial_r[m] )      (y: bf16 [M], in place)
+ * Every rank ends with the same y. The same CTA owns the same rows on every rank
+ * (same matrix shape, same GPU model), so a CTA only waits for its namesakes.
+ * Buffers (all device memory, mapped into every rank's address space, e.g.
+ * symmetric memory or CUDA IPC; zeroed once before the first call):
+ *   recv[p]  rank p's receive buffer: 2 * world * M floats (two epochs x one slot
+ *            per source rank), M up to the largest the buffers were sized for;
+ *   flags[p] rank p's flag words: world * CHR_NF4_AR_MAX_CTAS uint32;
+ *   epoch    this rank's own uint32[2] {calls completed, exit ticket};
+ *   status   this rank's own int32, set to 1 when a wait ran out of polls
+ *            (2^22; the sum then includes whatever had arrived).
+ * All ranks must issue the same sequence of calls on these buffers and tile the
+ * rows alike: when the ranks' K shares differ, each passes the largest K_pad of
+ * the layer in shape_k_pad. Capturable
+ * (the epoch lives in device memory). No counterpart in the reference. */
+#define CHR_NF4_AR_MAX_RANKS 8
+#define CHR_NF4_AR_MAX_CTAS 256
+
+typedef struct {
+  int32_t rank, world;
+  int32_t shape_k_pad; /* 0, or the largest K_pad any rank holds for this layer (uneven shares) */
+  int32_t reserved;
+  void *recv[CHR_NF4_AR_MAX_RANKS];
+  void *flags[CHR_NF4_AR_MAX_RANKS];
+  void *epoch;
+  void *status;
+} chr_nf4_peers_t;
+
+int chr_nf4_gemv_allreduce(const chr_nf4_dev_t *w, const void *x, void *y,
+                           const chr_nf4_peers_t *peers, const void *add, void *stream);
+
 /* Wide GEMM on activation rows: y_rows[N, M] = bf16( x_rows[N, K] . dequant(W)^T ),
  * the layout activations already have ([tokens, features], K contiguous), so no
  * transposes on either side and any N >= 1 in one call (tiled 16..256 columns per

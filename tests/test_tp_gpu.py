@@ -43,10 +43,17 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str) -> None:
         mode = loop.capture_graphs()
         graphed = loop.generate_device_window(prompt, 12).tokens
         chunked = loop.generate_device_window(prompt, 12, chunk=4).tokens
+        # the same shard with the row-split sums done over peer memory inside the GEMV launch
+        how = loop.state.enable_peer_exchange()
+        loop._graph, loop.graph_mode = None, "off"
+        p2p_eager = loop.generate_device_window(prompt, 12).tokens
+        p2p_mode = loop.capture_graphs()
+        p2p_graphed = loop.generate_device_window(prompt, 12).tokens
+        p2p = (how, p2p_eager, p2p_mode, loop.graph_error, p2p_graphed, loop.state.peers.timed_out())
         torch.cuda.synchronize()
         dist.barrier()
         with open(os.path.join(out_dir, f"r{rank}"), "w") as f:
-            f.write(repr((want, eager, mode, loop.graph_error, graphed, chunked)))
+            f.write(repr((want, eager, mode, loop.graph_error, graphed, chunked, p2p)))
             f.flush()
             os.fsync(f.fileno())
         loop.state.comm.shutdown(loop)
@@ -61,7 +68,12 @@ def test_tp2_matches_single_gpu(tmp_path):
     world = 2
     mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
-        want, eager, mode, err, graphed, chunked = eval((tmp_path / f"r{r}").read_text())
+        want, eager, mode, err, graphed, chunked, p2p = eval((tmp_path / f"r{r}").read_text())
         assert mode == "decodev2", err
         # FP32 partials summed before the single rounding: same ids as one GPU on this model
         assert eager == want and graphed == want and chunked[:4] == want[:4]
+        how, p2p_eager, p2p_mode, p2p_err, p2p_graphed, timed_out = p2p
+        print(f"rank {r}: peer buffers via {how}")
+        assert p2p_mode == "decodev2", p2p_err
+        assert not timed_out
+        assert p2p_eager == want and p2p_graphed == want
