@@ -50,18 +50,25 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
   const int tid = threadIdx.x;
   const uint32_t tab_lane = tab_base + static_cast<uint32_t>(tid & 31) * 8u;
   const int M = a.n_rows;
+  pdl_trigger();  // the next kernel of the chain may build its table meanwhile
 
-  // Nobody writes the epoch word before every CTA of this launch has taken its exit
-  // ticket, so all CTAs (and, call for call, all ranks) agree on e.
-  const unsigned int e = *reinterpret_cast<volatile unsigned int *>(pa.epoch) + 1u;
-  const size_t half = static_cast<size_t>(e & 1u) * pa.world * M;
-  float *mine = pa.recv[pa.rank] + half + static_cast<size_t>(pa.rank) * M;
-
+  // The epoch is read once the previous kernel of the stream has completed (and with
+  // it every earlier one): nobody writes the word before every CTA of the previous
+  // call has taken its exit ticket, so all CTAs (and, call for call, all ranks) agree.
+  unsigned int e = 0;
+  size_t half = 0;
+  float *mine = nullptr;
   GemvArgs b = a;
-  b.y32 = mine;  // the partial lands in this rank's own slot first
   gemv_run<R, C, 0>(b, reinterpret_cast<float *>(smem),
                     reinterpret_cast<__nv_bfloat16 *>(smem + kPartBytes), tab_lane, blockIdx.x,
-                    gridDim.x, [&] { build_pair_table(tab_base, tid, blockDim.x); });
+                    gridDim.x, [&] {
+                      build_pair_table(tab_base, tid, blockDim.x);
+                      pdl_wait();  // x and the residual belong to the previous kernel until it ends
+                      e = *reinterpret_cast<volatile unsigned int *>(pa.epoch) + 1u;
+                      half = static_cast<size_t>(e & 1u) * pa.world * M;
+                      mine = pa.recv[pa.rank] + half + static_cast<size_t>(pa.rank) * M;
+                      b.y32 = mine;  // the partial lands in this rank's own slot first
+                    });
   __syncthreads();  // this CTA's rows are stored
 
   // Rows of this CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of G*R rows.
@@ -83,7 +90,8 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
     __threadfence_system();
     for (int p = 0; p < pa.world; ++p) {
       if (p != pa.rank) {
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pa.flags[p] + slot), "r"(e)
+        // the fence above is the release; the flag itself is a relaxed store
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(pa.flags[p] + slot), "r"(e)
                      : "memory");
       }
     }
@@ -96,7 +104,7 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
     // peer is gone: do not spend the full poll budget again on every call
     const bool give_up = *reinterpret_cast<volatile int *>(pa.status) != 0;
     for (; !give_up;) {
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
       // epochs only grow; the difference form survives the 32-bit wrap
       if (static_cast<int>(seen - e) >= 0) break;
       if (++polls >= kPeerPolls) {
@@ -314,7 +322,10 @@ extern "C" int chr_nf4_gemv_allreduce(const chr_nf4_dev_t *w, const void *x, voi
       }                                                                                      \
       attr_bytes = smem_bytes;                                                               \
     }                                                                                        \
-    nf4_gemv_ar_kernel<RR, CC><<<grid, block, smem_bytes, st>>>(a, pa);                      \
+    if (launch_chain(nf4_gemv_ar_kernel<RR, CC>, grid, block, smem_bytes, st, a, pa) !=      \
+        cudaSuccess) {                                                                       \
+      return kLaunch;                                                                        \
+    }                                                                                        \
   } while (0)
 
   if (sh.C == 2) {
