@@ -219,7 +219,13 @@ def run_ours(args, spec) -> None:
     state = loop.state
 
     # prefill (timed apart), leaves next_token ready; one untimed pass first so that
-    # lazily loaded kernels and torch's attention setup are not in the timed window
+    # lazily loaded kernels and torch's attention setup are not in the timed window. On one
+    # GPU that pass also captures the chunk, and the timed pass replays it (a prompt shape
+    # that comes back); --eager-prefill times the Python-issued chunk instead.
+    prefill_mode = "eager"
+    if world == 1 and not args.eager_prefill:
+        loop.enable_prefill_graphs()
+        prefill_mode = "captured chunk graph, replayed"
     loop.reset()
     loop.prefill_from(prompt, 0)
     loop.reset()
@@ -360,6 +366,7 @@ def run_ours(args, spec) -> None:
         line["roofline"] = gemv_roof
         line["step_mode"] = f"launch chain ({fused_why})"
     line["config"]["row_split_exchange"] = exchange
+    line["config"]["prefill"] = prefill_mode
     if not args.no_cpu:
         cb = cpu_layer_sample(full_spec)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -378,6 +385,8 @@ def main() -> None:
     ap.add_argument("--model", default="qwen2.5-3b-arch")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--eager-prefill", action="store_true",
+                    help="time the prefill as issued from Python instead of as a replayed chunk graph")
     ap.add_argument("--nccl", action="store_true",
                     help="N > 1: sum the row-split partials with NCCL all-reduce launches instead of "
                          "inside the GEMV launch over peer memory")

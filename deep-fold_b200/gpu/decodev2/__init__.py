@@ -11,7 +11,7 @@ from .linear import (DeviceLayer, DeviceLinear, DeviceWeights, linear_backend, n
                      set_linear_backend)
 from .prefill import forward_prefill, prefill_chunk_width
 from .rope import apply_rope_torch, rope_tables_numpy, rope_tables_torch
-from .runner import consume_prompt, generate
+from .runner import PrefillGraphs, consume_prompt, generate
 from .session import DecodeV2Loop, Generation
 from .state import Arena, DecodeState, GraphSafeKV
 from .step import forward_decode, greedy_decode, set_fuse_rms, teacher_force_token
@@ -19,6 +19,7 @@ from .synth import Nf4Matrix, SynthLayer, SynthModel, build
 from .tp import Comm, shard_weights
 
 __all__ = [
+    "PrefillGraphs",
     "FusedStep",
     "fused_step_supported",
     "ArchSpec", "Arena", "CONFIGS", "DecodeState", "DecodeV2Loop", "DeviceLayer", "DeviceLinear",

@@ -25,6 +25,7 @@ __all__ = [
     "DeviceLinear",
     "DeviceLayer",
     "DeviceWeights",
+    "adjoin_rows",
     "linear_backend",
     "nf4_linear",
     "set_linear_backend",
@@ -132,6 +133,29 @@ def nf4_linear(mat: DeviceLinear, x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def adjoin_rows(mats: list[DeviceLinear]) -> DeviceLinear:
+    """Re-home matrices that share K into one contiguous blob and return the matrix whose
+    rows are theirs in order. The given handles become row views of the blob (no second
+    copy stays alive), so the N = 1 path keeps addressing them one by one while a wide
+    GEMM can take them all in a single pass over the activations."""
+    k, kp = mats[0].K, mats[0].K_pad
+    if any(m.K != k or m.K_pad != kp for m in mats):
+        raise ValueError("matrices to adjoin must share K")
+    packed = torch.cat([m.packed for m in mats], dim=0)
+    scale = torch.cat([m.scale for m in mats], dim=0)
+    bias = None
+    if any(m.bias is not None for m in mats):
+        ref = next(m.bias for m in mats if m.bias is not None)
+        bias = torch.cat([m.bias if m.bias is not None else torch.zeros(m.M, dtype=ref.dtype,
+                                                                        device=ref.device)
+                          for m in mats])
+    lo = 0
+    for m in mats:
+        m.packed, m.scale = packed[lo:lo + m.M], scale[lo:lo + m.M]
+        lo += m.M
+    return DeviceLinear(packed, scale, lo, k, kp, bias)
+
+
 @dataclass
 class DeviceLayer:
     norm1: torch.Tensor
@@ -144,6 +168,16 @@ class DeviceLayer:
     gate: DeviceLinear
     up: DeviceLinear
     down: DeviceLinear
+    qkv_rows: DeviceLinear | None = None   # q, k, v stacked (set by adjoin)
+    gate_up: DeviceLinear | None = None    # gate, up stacked (set by adjoin)
+
+    def adjoin(self) -> "DeviceLayer":
+        """Stack q/k/v and gate/up in memory so that the prefill runs each group as one GEMM."""
+        if self.q is not None and self.qkv_rows is None:
+            self.qkv_rows = adjoin_rows([self.q, self.k, self.v])
+        if self.gate_up is None:
+            self.gate_up = adjoin_rows([self.gate, self.up])
+        return self
 
 
 @dataclass
@@ -172,7 +206,7 @@ class DeviceWeights:
         else:
             embed = vec(model.embed)
         return cls(model.spec, embed, vec(model.final_norm), up(model.lm_head),
-                   [layer(ly) for ly in model.layers])
+                   [layer(ly).adjoin() for ly in model.layers])
 
     @classmethod
     def random_init(cls, spec: ArchSpec, seed: int, device="cuda",
@@ -197,7 +231,7 @@ class DeviceWeights:
             else:
                 wqkv = rnd(spec.wqkv_out, h)
             layers.append(DeviceLayer(ones(h), ones(h), q, k, v, wqkv, rnd(h, spec.q_dim),
-                                      rnd(inter, h), rnd(inter, h), rnd(h, inter)))
+                                      rnd(inter, h), rnd(inter, h), rnd(h, inter)).adjoin())
         table = rnd(spec.vocab, h)
         embed = PackedEmbed(table.packed, table.scale, spec.vocab, h)
         lm_head = table if spec.tied_embed else rnd(spec.vocab, h)

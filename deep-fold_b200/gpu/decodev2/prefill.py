@@ -38,6 +38,12 @@ def _split_qkv(layer: DeviceLayer, h: torch.Tensor, spec: ArchSpec):
         y = nf4_linear(layer.wqkv, h).view(n, spec.n_kv, spec.n_rep + 2, spec.head_dim)
         q = y[:, :, : spec.n_rep].reshape(n, spec.n_q, spec.head_dim)
         return q, y[:, :, -2], y[:, :, -1]
+    if layer.qkv_rows is not None:  # q, k, v stacked in memory: one pass over the activations
+        y = nf4_linear(layer.qkv_rows, h)
+        mq, mk = layer.q.M, layer.k.M
+        return (y[:, :mq].reshape(n, spec.n_q, spec.head_dim),
+                y[:, mq:mq + mk].reshape(n, -1, spec.head_dim),
+                y[:, mq + mk:].reshape(n, -1, spec.head_dim))
     return (
         nf4_linear(layer.q, h).view(n, spec.n_q, spec.head_dim),
         nf4_linear(layer.k, h).view(n, spec.n_kv, spec.head_dim),
@@ -90,8 +96,12 @@ def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch
         k_all, v_all = state.kv.view(li, seq)
         x = x + _reduced(state, nf4_linear(layer.o, _attend(q, k_all, v_all, spec, mask)))
         h = F.rms_norm(x, layer.norm2.shape, layer.norm2, spec.rms_eps)
-        x = x + _reduced(state, nf4_linear(
-            layer.down, F.silu(nf4_linear(layer.gate, h)) * nf4_linear(layer.up, h)))
+        if layer.gate_up is not None:
+            gu = nf4_linear(layer.gate_up, h)
+            act = F.silu(gu[:, : layer.gate.M]) * gu[:, layer.gate.M:]
+        else:
+            act = F.silu(nf4_linear(layer.gate, h)) * nf4_linear(layer.up, h)
+        x = x + _reduced(state, nf4_linear(layer.down, act))
     state.position.fill_(seq)
     state.valid_len.fill_(seq)
     if not logits:

@@ -12,11 +12,55 @@ from .prefill import forward_prefill, prefill_chunk_width
 from .state import DecodeState
 from .step import greedy_decode
 
-__all__ = ["consume_prompt", "generate"]
+__all__ = ["PrefillGraphs", "consume_prompt", "generate"]
+
+
+class PrefillGraphs:
+    """Prefill chunks as CUDA graphs, keyed by (start slot, length, logits wanted).
+
+    A prefill chunk is ~30 small launches per layer around the GEMMs, issued from
+    Python; for a prompt shape that comes back (same length bucket, same start) the
+    whole chunk replays as one graph instead. The first time a shape is seen it runs
+    eagerly (which also warms every kernel) and is then captured for the next time;
+    the token ids live in a static device buffer the replay reads. At most
+    ``max_entries`` shapes are kept (least recently used goes first). Single GPU only.
+    """
+
+    def __init__(self, state: DecodeState, weights: DeviceWeights, max_entries: int = 4) -> None:
+        if state.spec.tp != 1:
+            raise RuntimeError("prefill graphs are single-GPU")
+        self.state, self.weights, self.max_entries = state, weights, int(max_entries)
+        self._cache: dict = {}
+        self.replays = 0
+
+    def run(self, ids: torch.Tensor, start: int, logits: bool) -> None:
+        key = (int(start), int(ids.numel()), bool(logits))
+        entry = self._cache.pop(key, None)
+        if entry is not None:
+            static_ids, graph = entry
+            static_ids.copy_(ids)
+            graph.replay()
+            self.replays += 1
+            self._cache[key] = entry  # most recently used last
+            return
+        forward_prefill(self.state, self.weights, ids, start=start, logits=logits)
+        static_ids = ids.clone()
+        graph = torch.cuda.CUDAGraph()
+        main = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                forward_prefill(self.state, self.weights, static_ids, start=start, logits=logits)
+        main.wait_stream(side)
+        while len(self._cache) >= self.max_entries:
+            self._cache.pop(next(iter(self._cache)))
+        self._cache[key] = (static_ids, graph)
 
 
 def consume_prompt(state: DecodeState, weights: DeviceWeights, token_ids: Sequence[int], *,
-                   chunk: int | None = None, start: int = 0) -> None:
+                   chunk: int | None = None, start: int = 0,
+                   graphs: PrefillGraphs | None = None) -> None:
     """Fill KV for ``token_ids`` starting at slot ``start`` (0 = cold prompt after ``reset``)."""
     if not len(token_ids):
         raise ValueError("prompt must be non-empty")
@@ -30,7 +74,10 @@ def consume_prompt(state: DecodeState, weights: DeviceWeights, token_ids: Sequen
     buf = torch.tensor(ids, dtype=torch.long, device=state.device)
     for lo in range(0, len(ids), width):
         hi = min(lo + width, len(ids))
-        forward_prefill(state, weights, buf[lo:hi], start=pos + lo, logits=(hi == len(ids)))
+        if graphs is not None:
+            graphs.run(buf[lo:hi], pos + lo, hi == len(ids))
+        else:
+            forward_prefill(state, weights, buf[lo:hi], start=pos + lo, logits=(hi == len(ids)))
 
 
 def generate(state: DecodeState, weights: DeviceWeights, prompt_ids: Sequence[int], n_new: int, *,

@@ -21,7 +21,7 @@ from .fused import FusedStep, fused_step_supported
 from .graph import capture_greedy
 from .linear import DeviceWeights
 from .prefill import prefill_chunk_width
-from .runner import consume_prompt
+from .runner import PrefillGraphs, consume_prompt
 from .state import DecodeState
 from .step import greedy_decode, teacher_force_token
 
@@ -70,6 +70,7 @@ class DecodeV2Loop:
         self.graph_error: str | None = None
         self._graph = None
         self._fused: FusedStep | None = None
+        self._prefill_graphs: PrefillGraphs | None = None
 
     @classmethod
     def from_weights(cls, weights: DeviceWeights, *, dtype: torch.dtype = torch.bfloat16,
@@ -103,7 +104,8 @@ class DecodeV2Loop:
             raise ValueError("empty prompt")
         if pos < 0 or pos + len(seq) > self.max_seq:
             raise ValueError(f"position {pos}+{len(seq)} past max_seq={self.max_seq}")
-        consume_prompt(self.state, self.weights, seq, start=pos, chunk=chunk)
+        consume_prompt(self.state, self.weights, seq, start=pos, chunk=chunk,
+                       graphs=self._prefill_graphs)
         return self.state.arena.logits[0]
 
     forward = prefill_from
@@ -132,6 +134,10 @@ class DecodeV2Loop:
         if why is None:
             self._fused = FusedStep(self.state, self.weights)
         return why
+
+    def enable_prefill_graphs(self, on: bool = True, max_entries: int = 4) -> None:
+        """Replay prefill chunks whose (start, length) has been seen before as CUDA graphs."""
+        self._prefill_graphs = PrefillGraphs(self.state, self.weights, max_entries) if on else None
 
     @property
     def fused(self) -> bool:

@@ -287,3 +287,21 @@ def test_persistent_step_flags_a_bad_token_id_and_refuses_shards():
     with pytest.raises(RuntimeError):
         step(state, DeviceWeights.from_synth(build(TINY_LLAMA, 0), "cuda", torch.bfloat16))
     assert fused_step_supported(state, weights) is None
+
+
+def test_prefill_graphs_replay_equals_eager():
+    _, state, weights = session(MEDIUM_LLAMA, 0)
+    loop = DecodeV2Loop(state, weights)
+    prompt = [1, 3, 5, 7, 2, 9, 4]
+    want = loop.generate_device_window(prompt, 6).tokens
+    want_k = state.kv.k.clone()
+    loop.enable_prefill_graphs()
+    first = loop.generate_device_window(prompt, 6).tokens        # eager + capture
+    again = loop.generate_device_window(prompt, 6).tokens        # replay
+    other = loop.generate_device_window([9, 8, 7, 6, 5, 4, 3], 6).tokens   # same shape, new ids
+    assert loop._prefill_graphs.replays == 2
+    assert first == want and again == want
+    loop.enable_prefill_graphs(False)
+    assert other == loop.generate_device_window([9, 8, 7, 6, 5, 4, 3], 6).tokens
+    loop.generate_device_window(prompt, 6)
+    assert torch.equal(state.kv.k, want_k)
