@@ -95,6 +95,47 @@ def test_shards_reassemble_the_full_matrices():
         shard_linear_cols(cpu_linear(model.layers[0].q), 0, 3)
 
 
+@pytest.mark.parametrize("world", [4, 8])
+def test_uneven_shares_and_replicated_kv_heads_reproduce_one_layer(world):
+    """704 = 11 NF4 groups do not divide by 4 or 8 and 2 kv heads are fewer than the ranks:
+    the per-rank MLP partials still sum to the full product and every rank's q heads sit
+    next to the kv head they attend."""
+    import dataclasses
+
+    spec = dataclasses.replace(MEDIUM_LLAMA, name="uneven", n_layers=1, intermediate=704)
+    model = build(spec, 3)
+    full = cpu_weights(model)
+    shards = [shard_weights(full, r, world) for r in range(world)]
+    ly = full.layers[0]
+    rng = np.random.default_rng(5)
+    h = rng.standard_normal(spec.hidden)
+    silu = lambda t: t / (1.0 + np.exp(-t))
+    want = deq(ly.down).astype(np.float64) @ (silu(deq(ly.gate).astype(np.float64) @ h)
+                                               * (deq(ly.up).astype(np.float64) @ h))
+    acc = np.zeros(spec.hidden)
+    covered = 0
+    for r, sh in enumerate(shards):
+        part = sh.layers[0]
+        lo, hi = group_range(spec.intermediate, world, r)
+        assert lo % 64 == 0 and hi % 64 == 0 and part.gate.M == hi - lo == part.down.K
+        covered += hi - lo
+        act = silu(deq(part.gate).astype(np.float64) @ h) * (deq(part.up).astype(np.float64) @ h)
+        acc += deq(part.down).astype(np.float64) @ act
+        # attention: this rank's q heads and the kv head stored beside them
+        heads = spec.n_q // world
+        first = r * heads
+        assert np.array_equal(deq(part.q), deq(ly.q)[first * spec.head_dim:(first + heads) * spec.head_dim])
+        kvh = first // spec.n_rep
+        assert (first + heads - 1) // spec.n_rep == kvh
+        assert np.array_equal(deq(part.k), deq(ly.k)[kvh * spec.head_dim:(kvh + 1) * spec.head_dim])
+        assert np.array_equal(deq(part.v), deq(ly.v)[kvh * spec.head_dim:(kvh + 1) * spec.head_dim])
+        assert sh.spec.n_kv == 1 and sh.spec.n_q == heads
+    assert covered == spec.intermediate
+    np.testing.assert_allclose(acc, want, rtol=1e-10, atol=1e-12)
+    sizes = {sh.layers[0].down.K for sh in shards}
+    assert len(sizes) == 2  # the shares really are uneven
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
