@@ -123,10 +123,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
+// Two floats rounded to nearest-even bf16 in one conversion; lo lands in the low half.
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  const uint32_t a = __bfloat16_as_ushort(__float2bfloat16(lo));
-  const uint32_t b = __bfloat16_as_ushort(__float2bfloat16(hi));
-  return a | (b << 16);
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&v);
 }
 
 // ---- kernel -------------------------------------------------------------------
@@ -411,8 +411,16 @@ int bn_for(int N) { return N <= 16 ? 16 : (N <= 32 ? 32 : 64); }
 // per W row, 32 codes each), which keeps the codebook work ahead of the tensor core
 // at BN up to 256; the epilogue writes the transposed tile (consecutive lanes own
 // consecutive m, so every store instruction covers 64 contiguous bytes).
-constexpr int rThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 dequant + epilogue
-constexpr int rDequant = 256;
+#ifndef CHR_ROWS_DEQ_WARPS
+#define CHR_ROWS_DEQ_WARPS 16
+#endif
+// warp 0 TMA, warp 1 MMA, then the dequant + epilogue warps: 128 rows x rParts threads
+// per row. The dequant chain (lookup -> multiply -> round -> store) is latency-bound,
+// so more warps per scheduler keep it ahead of the tensor core.
+constexpr int rDequant = CHR_ROWS_DEQ_WARPS * 32;
+constexpr int rParts = rDequant / 128;          // threads per weight row (2 or 4)
+constexpr int rThreads = 64 + rDequant;
+static_assert(rParts == 2 || rParts == 4, "dequant warps: 8 or 16");
 
 __host__ __device__ constexpr int rows_stage_bytes(int bn) { return tRawBytes + tABytes + bn * tBK * 2; }
 __host__ __device__ constexpr int rows_stages(int bn) { return bn > 128 ? 4 : 6; }
@@ -518,10 +526,12 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
       }
     }
   } else {
-    // ---------------- dequant: thread (row r, half h) owns 32 codes ----------------
-    const int t = tid - 64;                 // 0..255
+    // -------- dequant: thread (row r, part) owns 64 / rParts codes of the K tile --------
+    constexpr int kBytes = 32 / rParts;     // packed bytes per thread per K tile
+    constexpr int kChunks = kBytes / 4;     // 8-code chunks (16 bytes of bf16 out)
+    const int t = tid - 64;
     const int r = t & 127;
-    const int hlf = t >> 7;
+    const int part = t >> 7;
     const int grow = m0 + r;
     const bool row_live = grow < M;
     const int n_groups = K_pad / kGroup;
@@ -541,24 +551,32 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
       if (!ok) break;
       ok = mbar_wait(in_full(s), (i / kStages) & 1);
       if (!ok) break;
-      uint4 pk;
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w)
-                   : "r"(raw_tile(s) + r * 32 + hlf * 16));
-      const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
-      const int k_base = kt * tBK + hlf * 32;
+      uint32_t wv[kChunks];
+      if constexpr (kChunks == 4) {
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(wv[0]), "=r"(wv[1]), "=r"(wv[2]), "=r"(wv[3])
+                     : "r"(raw_tile(s) + r * 32 + part * kBytes));
+      } else {
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];"
+                     : "=r"(wv[0]), "=r"(wv[1])
+                     : "r"(raw_tile(s) + r * 32 + part * kBytes));
+      }
+      const int k_base = kt * tBK + part * (64 / rParts);
+      const bool whole = k_base + 64 / rParts <= K;  // no K tail inside this thread's codes
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        const int c = hlf * 4 + c4;
+      for (int c4 = 0; c4 < kChunks; ++c4) {
+        const int c = part * kChunks + c4;
         uint32_t o[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const uint32_t byte = (wv[c4] >> (8 * e)) & 0xFFu;
-          const int k = k_base + c4 * 8 + 2 * e;
           float lo = lut[byte & 0xFu] * sc;
           float hi = lut[byte >> 4] * sc;
-          if (k >= K) lo = 0.f;
-          if (k + 1 >= K) hi = 0.f;
+          if (!whole) {
+            const int k = k_base + c4 * 8 + 2 * e;
+            if (k >= K) lo = 0.f;
+            if (k + 1 >= K) hi = 0.f;
+          }
           o[e] = pack_bf16(lo, hi);
         }
         const uint32_t dst = a_tile(s) + a_row_off + static_cast<uint32_t>((c ^ sw) * 16);
@@ -578,11 +596,13 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
     if (ok && n_local > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int quad = warp & 3;
-      const int col_half = (warp - 2) >> 2;   // warps 2..5 -> 0, 6..9 -> 1
+      // the column range is shared out over the warps of a quadrant, 16 columns at least
+      constexpr int kColGroups = (rDequant / 128) < (BN / 16) ? (rDequant / 128) : (BN / 16);
+      constexpr int kPerGroup = BN / kColGroups;
+      const int col_group = (warp - 2) >> 2;
+      const int c_begin = col_group * kPerGroup;
+      const int c_end = col_group < kColGroups ? c_begin + kPerGroup : c_begin;
       const int row = m0 + quad * 32 + lane;
-      constexpr int kHalf = BN / 2 >= 16 ? BN / 2 : 16;
-      const int c_begin = BN >= 32 ? col_half * kHalf : 0;
-      const int c_end = BN >= 32 ? c_begin + kHalf : (col_half == 0 ? BN : 0);
       for (int c0 = c_begin; c0 < c_end; c0 += 16) {
         uint32_t v[16];
         tmem_ld16(tmem_d + (static_cast<uint32_t>(quad * 32) << 16) + c0, v);
