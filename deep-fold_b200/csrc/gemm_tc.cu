@@ -26,6 +26,8 @@
 #include <cuda.h>
 
 #include "gemm_plan.h"
+#include <cstdlib>
+
 #include "nf4_common.cuh"
 
 namespace chr {
@@ -418,25 +420,36 @@ int bn_for(int N) { return N <= 16 ? 16 : (N <= 32 ? 32 : 64); }
 // per row. The dequant chain (lookup -> multiply -> round -> store) is latency-bound,
 // so more warps per scheduler keep it ahead of the tensor core.
 constexpr int rDequant = CHR_ROWS_DEQ_WARPS * 32;
-constexpr int rParts = rDequant / 128;          // threads per weight row (2 or 4)
 constexpr int rThreads = 64 + rDequant;
-static_assert(rParts == 2 || rParts == 4, "dequant warps: 8 or 16");
+static_assert(rDequant == 256 || rDequant == 512, "dequant warps: 8 or 16");
+// MT: 128-row weight tiles per CTA. With two, a CTA multiplies 256 rows by the same
+// activation tile (two TMEM accumulators), which halves the activation bytes pulled
+// from L2 per flop: at MT = 1 and BN = 256 every K tile needs 36 KB per CTA, 6.5 TB/s
+// over the chip at the rate measured, which is where the kernel stopped scaling.
 
-__host__ __device__ constexpr int rows_stage_bytes(int bn) { return tRawBytes + tABytes + bn * tBK * 2; }
-__host__ __device__ constexpr int rows_stages(int bn) { return bn > 128 ? 4 : 6; }
-__host__ __device__ constexpr int rows_smem_bytes(int bn) {
-  return rows_stages(bn) * rows_stage_bytes(bn) + 1024 + 256;
+__host__ __device__ constexpr int rows_stage_bytes(int bn, int mt = 1) {
+  return mt * (tRawBytes + tABytes) + bn * tBK * 2;
+}
+__host__ __device__ constexpr int rows_stages(int bn, int mt = 1) {
+  return mt > 1 ? 3 : (bn > 128 ? 4 : 6);
+}
+__host__ __device__ constexpr int rows_smem_bytes(int bn, int mt = 1) {
+  return rows_stages(bn, mt) * rows_stage_bytes(bn, mt) + 1024 + 256;
 }
 
-template <int BN>
+template <int BN, int MT>
 __global__ void __launch_bounds__(rThreads, 1)
 gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
                  const __grid_constant__ CUtensorMap x_map, const uint16_t *__restrict__ scale,
                  __nv_bfloat16 *__restrict__ y, float *__restrict__ partial, int M, int K,
                  int K_pad, int N, int n_ktiles, int tiles_per_split) {
-  constexpr int kStages = rows_stages(BN);
+  constexpr int kStages = rows_stages(BN, MT);
   constexpr int kBBytes = BN * tBK * 2;
-  constexpr uint32_t kCols = BN < 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+  constexpr int kABytes = MT * tABytes;
+  constexpr int kRawBytes = MT * tRawBytes;
+  constexpr uint32_t kAccCols = BN < 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+  constexpr uint32_t kCols = kAccCols * MT;
+  static_assert(kCols <= 512, "TMEM columns");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float lut[16];
   __shared__ uint32_t tmem_slot;
@@ -444,17 +457,17 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int m0 = blockIdx.x * tBM;
+  const int m0 = blockIdx.x * tBM * MT;
   const int n0 = blockIdx.y * BN;
   const int kt0 = blockIdx.z * tiles_per_split;
   const int kt1 = min(n_ktiles, kt0 + tiles_per_split);
   const int n_local = kt1 - kt0;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  auto a_tile = [&](int s) { return base + s * tABytes; };
-  auto b_tile = [&](int s) { return base + kStages * tABytes + s * kBBytes; };
-  auto raw_tile = [&](int s) { return base + kStages * (tABytes + kBBytes) + s * tRawBytes; };
-  const uint32_t bars = base + kStages * rows_stage_bytes(BN);
+  auto a_tile = [&](int s) { return base + s * kABytes; };  // MT tiles of tABytes each
+  auto b_tile = [&](int s) { return base + kStages * kABytes + s * kBBytes; };
+  auto raw_tile = [&](int s) { return base + kStages * (kABytes + kBBytes) + s * kRawBytes; };
+  const uint32_t bars = base + kStages * rows_stage_bytes(BN, MT);
   auto in_full = [&](int s) { return bars + 8 * s; };                   // TMA: codes + x tile
   auto ab_full = [&](int s) { return bars + 8 * (kStages + s); };       // dequant done
   auto empty = [&](int s) { return bars + 8 * (2 * kStages + s); };     // MMA done with stage
@@ -489,7 +502,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
         const int s = i % kStages;
         if (i >= kStages) ok = mbar_wait(empty(s), ((i / kStages) - 1) & 1);
         if (!ok) break;
-        mbar_expect_tx(in_full(s), tRawBytes + kBBytes);
+        mbar_expect_tx(in_full(s), kRawBytes + kBBytes);
         tma_load_2d(raw_tile(s), &packed_map, in_full(s), (kt0 + i) * (tBK / 2), m0);
         tma_load_2d(b_tile(s), &x_map, in_full(s), (kt0 + i) * tBK, n0);
         issued = i + 1;
@@ -513,9 +526,12 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int k4 = 0; k4 < tBK / 16; ++k4) {
-          umma_bf16(tmem_d, umma_desc(a_tile(s) + k4 * 32), umma_desc(b_tile(s) + k4 * 32), idesc,
-                    (i > 0 || k4 > 0) ? 1u : 0u);
+        for (int ti = 0; ti < MT; ++ti) {
+#pragma unroll
+          for (int k4 = 0; k4 < tBK / 16; ++k4) {
+            umma_bf16(tmem_d + ti * kAccCols, umma_desc(a_tile(s) + ti * tABytes + k4 * 32),
+                      umma_desc(b_tile(s) + k4 * 32), idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+          }
         }
         umma_commit(empty(s));
       }
@@ -527,16 +543,21 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
     }
   } else {
     // -------- dequant: thread (row r, part) owns 64 / rParts codes of the K tile --------
+    constexpr int kRows = tBM * MT;
+    constexpr int rParts = rDequant / kRows;  // threads per weight row
+    static_assert(rParts == 1 || rParts == 2 || rParts == 4, "threads per row");
     constexpr int kBytes = 32 / rParts;     // packed bytes per thread per K tile
     constexpr int kChunks = kBytes / 4;     // 8-code chunks (16 bytes of bf16 out)
     const int t = tid - 64;
-    const int r = t & 127;
-    const int part = t >> 7;
+    const int r = t % kRows;                // row inside the CTA's MT tiles
+    const int part = t / kRows;
     const int grow = m0 + r;
     const bool row_live = grow < M;
     const int n_groups = K_pad / kGroup;
-    const uint32_t a_row_off = static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
-    const int sw = r & 7;
+    const int rr = r & (tBM - 1);           // row inside its 128-row tile
+    const uint32_t a_row_off = static_cast<uint32_t>((r / tBM) * tABytes + (rr >> 3) * 1024 +
+                                                     (rr & 7) * 128);
+    const int sw = rr & 7;
     bool ok = true;
     uint16_t s_bits = 0;
     if (row_live && n_local > 0) s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt0);
@@ -552,7 +573,14 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
       ok = mbar_wait(in_full(s), (i / kStages) & 1);
       if (!ok) break;
       uint32_t wv[kChunks];
-      if constexpr (kChunks == 4) {
+      if constexpr (kChunks == 8) {
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(wv[0]), "=r"(wv[1]), "=r"(wv[2]), "=r"(wv[3])
+                     : "r"(raw_tile(s) + r * 32));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(wv[4]), "=r"(wv[5]), "=r"(wv[6]), "=r"(wv[7])
+                     : "r"(raw_tile(s) + r * 32 + 16));
+      } else if constexpr (kChunks == 4) {
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                      : "=r"(wv[0]), "=r"(wv[1]), "=r"(wv[2]), "=r"(wv[3])
                      : "r"(raw_tile(s) + r * 32 + part * kBytes));
@@ -596,16 +624,21 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
     if (ok && n_local > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int quad = warp & 3;
-      // the column range is shared out over the warps of a quadrant, 16 columns at least
-      constexpr int kColGroups = (rDequant / 128) < (BN / 16) ? (rDequant / 128) : (BN / 16);
-      constexpr int kPerGroup = BN / kColGroups;
+      // warps of a TMEM lane quadrant share out the MT accumulators' columns, 16 at least
+      constexpr int kWarpsPerQuad = rDequant / 128;
+      constexpr int kUnits = MT * (BN / 16);                       // 16-column units in all
+      constexpr int kGroups = kWarpsPerQuad < kUnits ? kWarpsPerQuad : kUnits;
+      constexpr int kPerGroup = kUnits / kGroups * 16;             // columns per warp
+      static_assert(kUnits % kGroups == 0 && BN % kPerGroup == 0, "epilogue split");
       const int col_group = (warp - 2) >> 2;
-      const int c_begin = col_group * kPerGroup;
-      const int c_end = col_group < kColGroups ? c_begin + kPerGroup : c_begin;
-      const int row = m0 + quad * 32 + lane;
+      const int g_begin = col_group * kPerGroup;                   // in the MT * BN column space
+      const int ti = g_begin / BN;
+      const int c_begin = g_begin - ti * BN;
+      const int c_end = col_group < kGroups ? c_begin + kPerGroup : c_begin;
+      const int row = m0 + ti * tBM + quad * 32 + lane;
       for (int c0 = c_begin; c0 < c_end; c0 += 16) {
         uint32_t v[16];
-        tmem_ld16(tmem_d + (static_cast<uint32_t>(quad * 32) << 16) + c0, v);
+        tmem_ld16(tmem_d + (static_cast<uint32_t>(quad * 32) << 16) + ti * kAccCols + c0, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < M) {
 #pragma unroll
@@ -642,17 +675,33 @@ __global__ void reduce_rows_kernel(const float *__restrict__ partial, __nv_bfloa
 }
 
 struct RowsPlan {
-  int bn, grid_x, grid_y, split, tiles_per_split, n_ktiles;
+  int bn, mt, grid_x, grid_y, split, tiles_per_split, n_ktiles;
   long long ws_floats;
 };
+
+int rows_force_mt() {  // CHR_NF4_ROWS_MT = 1 | 2 pins the M tiles per CTA (A/B runs)
+  static int cached = -1;
+  if (cached < 0) {
+    const char *env = std::getenv("CHR_NF4_ROWS_MT");
+    cached = (env != nullptr && (env[0] == '1' || env[0] == '2')) ? env[0] - '0' : 0;
+  }
+  return cached;
+}
 
 RowsPlan plan_rows(int M, int K_pad, int N, bool have_ws) {
   RowsPlan p{};
   const int n16 = ((N + 15) / 16) * 16;
   p.bn = n16 <= 32 ? 32 : (n16 <= 64 ? 64 : (n16 <= 128 ? 128 : 256));
   if (n16 <= 16) p.bn = 16;
-  p.grid_x = (M + tBM - 1) / tBM;
   p.grid_y = (N + p.bn - 1) / p.bn;
+  // two weight tiles per CTA once that still leaves at least two full waves of CTAs
+  p.mt = 1;
+  if (p.bn == 256) {
+    const int ctas2 = ((M + 2 * tBM - 1) / (2 * tBM)) * p.grid_y;
+    if (ctas2 >= 2 * sm_count()) p.mt = 2;
+    if (rows_force_mt() != 0) p.mt = rows_force_mt();
+  }
+  p.grid_x = (M + tBM * p.mt - 1) / (tBM * p.mt);
   p.n_ktiles = (K_pad + tBK - 1) / tBK;
   int want = 1;
   if (have_ws) {
@@ -668,7 +717,7 @@ RowsPlan plan_rows(int M, int K_pad, int N, bool have_ws) {
   return p;
 }
 
-template <int BN>
+template <int BN, int MT = 1>
 int launch_rows(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y, int N,
                 float *partial, const RowsPlan &p, cudaStream_t st) {
   EncodeTiled enc = encode_fn();
@@ -677,7 +726,7 @@ int launch_rows(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(w.K_pad / 2), static_cast<cuuint64_t>(w.M)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(w.K_pad / 2)};
-    const cuuint32_t box[2] = {tBK / 2, tBM};
+    const cuuint32_t box[2] = {tBK / 2, static_cast<cuuint32_t>(tBM * MT)};
     const cuuint32_t elem[2] = {1, 1};
     if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w.packed), dims, strides,
             box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -698,15 +747,15 @@ int launch_rows(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y
   }
   static bool attr_done = false;
   if (!attr_done) {
-    if (cudaFuncSetAttribute(gemm_rows_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             rows_smem_bytes(BN)) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_rows_kernel<BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             rows_smem_bytes(BN, MT)) != cudaSuccess) {
       return kLaunch;
     }
     attr_done = true;
   }
   const dim3 grid(static_cast<unsigned>(p.grid_x), static_cast<unsigned>(p.grid_y),
                   static_cast<unsigned>(p.split));
-  gemm_rows_kernel<BN><<<grid, rThreads, rows_smem_bytes(BN), st>>>(
+  gemm_rows_kernel<BN, MT><<<grid, rThreads, rows_smem_bytes(BN, MT), st>>>(
       wmap, xmap, w.scale, y, partial, w.M, w.K, w.K_pad, N, p.n_ktiles, p.tiles_per_split);
   if (partial != nullptr) {
     const long long total = static_cast<long long>(w.M) * N;
@@ -781,6 +830,8 @@ extern "C" int chr_nf4_gemm_rows(const chr_nf4_dev_t *w, const void *x_rows, voi
     case 32: return launch_rows<32>(*w, xb, yb, N, partial, p, st);
     case 64: return launch_rows<64>(*w, xb, yb, N, partial, p, st);
     case 128: return launch_rows<128>(*w, xb, yb, N, partial, p, st);
-    default: return launch_rows<256>(*w, xb, yb, N, partial, p, st);
+    default:
+      if (p.mt == 2) return launch_rows<256, 2>(*w, xb, yb, N, partial, p, st);
+      return launch_rows<256>(*w, xb, yb, N, partial, p, st);
   }
 }
