@@ -271,6 +271,23 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, AttnSmem<P, H> &sm,
   sync();
   if (!is_last) return;
   __threadfence();
+  // One round trip for the merge: every thread puts the loads of its partial sums in
+  // flight first, the splits' (m, l) are fetched and turned into softmax weights
+  // meanwhile, and the weighted sum runs on registers.
+  constexpr int kIters = H * 64 * P / kAttnThreads;
+  float pv[kIters][kAttnMaxSplit];
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    const int i = tid + it * kAttnThreads;
+    const int h = i / hd;
+    const int d = i - h * hd;
+    const float *oh = a.o_s + static_cast<size_t>(h_first + h) * n_split * hd + d;
+#pragma unroll
+    for (int sidx = 0; sidx < kAttnMaxSplit; ++sidx) {
+      pv[it][sidx] = (i < nh * hd && sidx < n_split) ? __ldcg(oh + static_cast<size_t>(sidx) * hd)
+                                                     : 0.f;
+    }
+  }
   // softmax weights of the splits, once per head: w[h][s] = exp(m_s - max) / sum
   float *wts = &sm_o[0][0][0];  // the combine buffer is free again
   for (int h = warp; h < nh; h += kAttnWarps) {
@@ -283,19 +300,19 @@ __device__ __forceinline__ void attn_item(const AttnArgs &a, AttnSmem<P, H> &sm,
     if (lane < kAttnMaxSplit) wts[h * kAttnMaxSplit + lane] = ll > 0.f ? wexp / ll : 0.f;
   }
   sync();
-  for (int i = tid; i < nh * hd; i += kAttnThreads) {
-    const int h = i / hd;
-    const int d = i - h * hd;
-    const float *oh = a.o_s + static_cast<size_t>(h_first + h) * n_split * hd + d;
-    float v[kAttnMaxSplit];
 #pragma unroll
-    for (int sidx = 0; sidx < kAttnMaxSplit; ++sidx) {
-      v[sidx] = sidx < n_split ? __ldcg(oh + static_cast<size_t>(sidx) * hd) : 0.f;
+  for (int it = 0; it < kIters; ++it) {
+    const int i = tid + it * kAttnThreads;
+    if (i < nh * hd) {
+      const int h = i / hd;
+      const int d = i - h * hd;
+      float oo = 0.f;
+#pragma unroll
+      for (int sidx = 0; sidx < kAttnMaxSplit; ++sidx) {
+        oo += wts[h * kAttnMaxSplit + sidx] * pv[it][sidx];
+      }
+      a.out[static_cast<size_t>(h_first + h) * hd + d] = __float2bfloat16(oo);
     }
-    float oo = 0.f;
-#pragma unroll
-    for (int sidx = 0; sidx < kAttnMaxSplit; ++sidx) oo += wts[h * kAttnMaxSplit + sidx] * v[sidx];
-    a.out[static_cast<size_t>(h_first + h) * hd + d] = __float2bfloat16(oo);
   }
 }
 
