@@ -4,6 +4,7 @@ from __future__ import annotations
 
 from .arch import (CONFIGS, INTERNLM25_20B, MEDIUM_LLAMA, QWEN25_3B, QWEN25_14B, QWEN25_32B,
                    TINY_INTERNLM, TINY_LLAMA, ArchSpec, shard_spec, with_max_seq)
+from .chrfile import load_weights, save_synth, tensor_names
 from .embed import PackedEmbed, bind_embed, gather_embed
 from .fused import FusedStep, fused_step_supported
 from .graph import GreedyGraph, capture_greedy
@@ -19,6 +20,9 @@ from .synth import Nf4Matrix, SynthLayer, SynthModel, build
 from .tp import Comm, shard_weights
 
 __all__ = [
+    "load_weights",
+    "save_synth",
+    "tensor_names",
     "PrefillGraphs",
     "FusedStep",
     "fused_step_supported",

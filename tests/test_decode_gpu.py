@@ -305,3 +305,25 @@ def test_prefill_graphs_replay_equals_eager():
     assert other == loop.generate_device_window([9, 8, 7, 6, 5, 4, 3], 6).tokens
     loop.generate_device_window(prompt, 6)
     assert torch.equal(state.kv.k, want_k)
+
+
+@pytest.mark.parametrize("spec,seed", [(MEDIUM_LLAMA, 0), (TINY_INTERNLM, 1)])
+def test_weights_loaded_from_a_chr_file_decode_like_the_model_they_came_from(tmp_path, spec, seed):
+    from gpu.decodev2 import load_weights, save_synth
+
+    model = build(spec, seed)
+    path = save_synth(model, str(tmp_path / "model.chr"))
+    loaded = load_weights(path, spec, "cuda")
+    direct = DeviceWeights.from_synth(model, "cuda", torch.bfloat16, packed_embed=True)
+    for a, b in zip(loaded.layers, direct.layers):
+        for name in ("q", "k", "v", "wqkv", "o", "gate", "up", "down"):
+            x, y = getattr(a, name), getattr(b, name)
+            assert (x is None) == (y is None)
+            if x is not None:
+                assert torch.equal(x.packed, y.packed) and torch.equal(x.scale, y.scale)
+    prompt = [1, 3, 5, 7, 2]
+    want = DecodeV2Loop.from_weights(direct).generate_device_window(prompt, 8).tokens
+    loop = DecodeV2Loop.from_weights(loaded)
+    assert loop.generate_device_window(prompt, 8).tokens == want
+    assert loop.capture_graphs() == "decodev2", loop.graph_error
+    assert loop.generate_device_window(prompt, 8).tokens == want
