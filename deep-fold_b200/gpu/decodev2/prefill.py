@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from gpu.nf4 import LIVE_MAX_N
+from gpu.nf4 import LIVE_MAX_N, nf4_rms_rows, nf4_rope_kv_rows, nf4_silu_mul
 
 from .arch import ArchSpec
 from .embed import gather_embed
@@ -18,7 +18,20 @@ from .linear import DeviceLayer, DeviceWeights, nf4_linear
 from .rope import apply_rope_torch
 from .state import DecodeState
 
-__all__ = ["forward_prefill", "prefill_chunk_width"]
+__all__ = ["forward_prefill", "prefill_chunk_width", "set_fused_rows", "fused_rows"]
+
+_FUSED_ROWS = True
+
+
+def fused_rows() -> bool:
+    return _FUSED_ROWS
+
+
+def set_fused_rows(on: bool) -> None:
+    """``True`` (default): RMSNorm, RoPE + cache write and SiLU*up of a chunk run as one
+    launch each; ``False``: as the reference's torch ops (same bits for RoPE and SiLU*up)."""
+    global _FUSED_ROWS
+    _FUSED_ROWS = bool(on)
 
 
 #: positions per prefill chunk when the caller does not say; the wide GEMM has no
@@ -87,18 +100,31 @@ def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch
     cos, sin = state.cos[start:seq], state.sin[start:seq]
     q_pos = torch.arange(start, seq, device=state.device).unsqueeze(1)
     mask = (torch.arange(seq, device=state.device).unsqueeze(0) <= q_pos)[None, None]
+    fused = _FUSED_ROWS and x.dtype is torch.bfloat16 and spec.hidden % 8 == 0
     for li, layer in enumerate(weights.layers):
-        h = F.rms_norm(x, layer.norm1.shape, layer.norm1, spec.rms_eps)
+        if fused:
+            h = nf4_rms_rows(x, layer.norm1, spec.rms_eps)
+        else:
+            h = F.rms_norm(x, layer.norm1.shape, layer.norm1, spec.rms_eps)
         q, k, v = _split_qkv(layer, h, spec)
-        q = apply_rope_torch(q, cos, sin)
-        k = apply_rope_torch(k, cos, sin)
-        state.kv.write_range(li, start, k, v)
+        if fused and layer.wqkv is None:
+            q = nf4_rope_kv_rows(q.flatten(1), k.flatten(1), v.flatten(1), state.kv.k[li],
+                                 state.kv.v[li], state.cos, state.sin, start, q.shape[1],
+                                 k.shape[1], spec.head_dim)
+        else:
+            q = apply_rope_torch(q, cos, sin)
+            k = apply_rope_torch(k, cos, sin)
+            state.kv.write_range(li, start, k, v)
         k_all, v_all = state.kv.view(li, seq)
         x = x + _reduced(state, nf4_linear(layer.o, _attend(q, k_all, v_all, spec, mask)))
-        h = F.rms_norm(x, layer.norm2.shape, layer.norm2, spec.rms_eps)
+        if fused:
+            h = nf4_rms_rows(x, layer.norm2, spec.rms_eps)
+        else:
+            h = F.rms_norm(x, layer.norm2.shape, layer.norm2, spec.rms_eps)
         if layer.gate_up is not None:
             gu = nf4_linear(layer.gate_up, h)
-            act = F.silu(gu[:, : layer.gate.M]) * gu[:, layer.gate.M:]
+            act = (nf4_silu_mul(gu, layer.gate.M) if fused
+                   else F.silu(gu[:, : layer.gate.M]) * gu[:, layer.gate.M:])
         else:
             act = F.silu(nf4_linear(layer.gate, h)) * nf4_linear(layer.up, h)
         x = x + _reduced(state, nf4_linear(layer.down, act))

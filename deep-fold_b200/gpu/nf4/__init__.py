@@ -37,6 +37,9 @@ __all__ = [
     "nf4_plan",
     "nf4_qkv",
     "nf4_rms",
+    "nf4_rms_rows",
+    "nf4_rope_kv_rows",
+    "nf4_silu_mul",
     "nf4_rope_kv",
     "nf4_set_pdl",
     "nf4_set_tuning",
@@ -626,3 +629,62 @@ def nf4_pick_commit(
         _ptr(finished), int(eos), _ptr(scratch), _stream(),
     )
     _lib.check(rc, "chr_nf4_pick_commit")
+
+
+# --------------------------------------------------------------------------- #
+# row-wise helpers of the chunked prefill
+# --------------------------------------------------------------------------- #
+def _rows_view(t: torch.Tensor, what: str) -> tuple[int, int]:
+    """(rows, row stride in elements) of a CUDA bf16 2-D view whose rows are contiguous."""
+    if not t.is_cuda or t.dtype is not torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+        _fail(f"{what} must be a CUDA bfloat16 [N, F] view with contiguous rows")
+    return int(t.size(0)), int(t.stride(0))
+
+
+def nf4_rms_rows(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm of every row of ``x`` ``[N, K]`` (rows may be strided) -> contiguous ``[N, K]``."""
+    n, stride = _rows_view(x, "x")
+    k = int(x.size(1))
+    wv = _opt_bf16(w, k, "w", exact=True)
+    y = torch.empty((n, k), dtype=torch.bfloat16, device=x.device)
+    rc = _lib.load().chr_nf4_rms_rows(_ptr(x), stride, _ptr(wv), _ptr(y), n, k, float(eps), _stream())
+    _lib.check(rc, "chr_nf4_rms_rows")
+    return y
+
+
+def nf4_rope_kv_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor,
+                     v_cache: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, start: int,
+                     n_q: int, n_kv: int, hd: int) -> torch.Tensor:
+    """RoPE for positions ``start..start+N-1``: rotated q ``[N, n_q, hd]`` (new tensor); k rotated
+    and v copied into cache rows ``start..`` of ``k_cache`` / ``v_cache`` ``[max_seq, n_kv, hd]``."""
+    n, qs = _rows_view(q, "q")
+    nk, ks = _rows_view(k, "k")
+    nv, vs = _rows_view(v, "v")
+    if nk != n or nv != n or q.size(1) != n_q * hd or k.size(1) != n_kv * hd or v.size(1) != n_kv * hd:
+        _fail("q / k / v rows do not match N, n_q, n_kv, hd")
+    for t, what in ((k_cache, "k_cache"), (v_cache, "v_cache"), (cos, "cos"), (sin, "sin")):
+        if not t.is_cuda or t.dtype is not torch.bfloat16 or not t.is_contiguous():
+            _fail(f"{what} must be contiguous CUDA bfloat16")
+    max_seq = int(k_cache.size(0))
+    if tuple(k_cache.shape) != (max_seq, n_kv, hd) or tuple(v_cache.shape) != (max_seq, n_kv, hd):
+        _fail("caches must be [max_seq, n_kv, hd]")
+    if cos.size(0) < int(start) + n or cos.size(-1) != hd or sin.shape != cos.shape:
+        _fail("cos / sin must cover the positions with hd columns")
+    q_out = torch.empty((n, n_q, hd), dtype=torch.bfloat16, device=q.device)
+    rc = _lib.load().chr_nf4_rope_kv_rows(
+        _ptr(q), qs, _ptr(k), ks, _ptr(v), vs, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(cos),
+        _ptr(sin), int(start), n, int(n_q), int(n_kv), int(hd), max_seq, _stream())
+    _lib.check(rc, "chr_nf4_rope_kv_rows")
+    return q_out
+
+
+def nf4_silu_mul(gate_up: torch.Tensor, inter: int) -> torch.Tensor:
+    """``silu(gate_up[:, :I]) * gate_up[:, I:]`` with bf16 rounding after each op -> ``[N, I]``."""
+    if (not gate_up.is_cuda or gate_up.dtype is not torch.bfloat16 or gate_up.dim() != 2
+            or not gate_up.is_contiguous() or gate_up.size(1) != 2 * int(inter)):
+        _fail("gate_up must be contiguous CUDA bfloat16 [N, 2*I]")
+    n = int(gate_up.size(0))
+    out = torch.empty((n, int(inter)), dtype=torch.bfloat16, device=gate_up.device)
+    rc = _lib.load().chr_nf4_silu_mul(_ptr(gate_up), _ptr(out), n, int(inter), _stream())
+    _lib.check(rc, "chr_nf4_silu_mul")
+    return out

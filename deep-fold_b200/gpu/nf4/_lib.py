@@ -137,6 +137,14 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     ),
+    "chr_nf4_rms_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_int32, c_float,
+                                 c_void_p]),
+    "chr_nf4_rope_kv_rows": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p],
+    ),
+    "chr_nf4_silu_mul": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "chr_nf4_decode_step": (c_int, [POINTER(ChrNf4Step), c_void_p]),
     "chr_nf4_decode_step_status": (c_int, [c_void_p]),
     "chr_nf4_encode_f32": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int32]),

@@ -255,6 +255,32 @@ int chr_nf4_decode_f32(const uint8_t *packed, const uint16_t *scale, int32_t M,
 int chr_nf4_encode_dev(const float *w, int32_t M, int32_t K, uint8_t *packed,
                        uint16_t *scale, int32_t *status, void *stream);
 
+/* ---- Row-wise helpers of the chunked prefill -------------------------------
+ * The elementwise work between a chunk's GEMMs, which the reference issues as
+ * torch ops in the cache dtype (gpu/decodev2/prefill.py:58-141); one launch each.
+ * No counterpart in the reference's C ABI. */
+
+/* y[n, :] = bf16( w * x[n, :] * rsqrt(mean(x[n, :]^2) + eps) ) for N rows of K bf16
+ * values; x rows x_stride elements apart (a multiple of 8), y contiguous. The same
+ * summation order as chr_nf4_rms and the GEMVs' fused RMSNorm. */
+int chr_nf4_rms_rows(const void *x, int64_t x_stride, const void *w, void *y, int32_t N,
+                     int32_t K, float eps, void *stream);
+
+/* RoPE for N consecutive positions start..start+N-1 and the cache write of the
+ * chunk: q [N, n_q, hd] (rows q_stride apart) is rotated into q_out (contiguous),
+ * k is rotated into k_cache rows, v copied into v_cache rows (caches bf16
+ * [max_seq, n_kv, hd]). bf16 arithmetic with a rounding after each product and
+ * after the sum, as torch's tensor math in bf16 does. */
+int chr_nf4_rope_kv_rows(const void *q, int64_t q_stride, const void *k, int64_t k_stride,
+                         const void *v, int64_t v_stride, void *q_out, void *k_cache,
+                         void *v_cache, const void *cos, const void *sin, int32_t start,
+                         int32_t N, int32_t n_q, int32_t n_kv, int32_t hd, int32_t max_seq,
+                         void *stream);
+
+/* out[n, i] = bf16( bf16(silu(g)) * u ) with g = gate_up[n, i], u = gate_up[n, I + i]:
+ * the activation on the output of the stacked gate/up GEMM (bf16 [N, 2*I]). */
+int chr_nf4_silu_mul(const void *gate_up, void *out, int32_t N, int32_t I, void *stream);
+
 /* ---- Whole greedy step in one persistent launch ---------------------------
  * The sequence the reference issues as one launch per operation
  * (gpu/decodev2/step.py:162-187: embed row -> per layer [RMSNorm + q/k/v GEMV,

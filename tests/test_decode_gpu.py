@@ -327,3 +327,23 @@ def test_weights_loaded_from_a_chr_file_decode_like_the_model_they_came_from(tmp
     assert loop.generate_device_window(prompt, 8).tokens == want
     assert loop.capture_graphs() == "decodev2", loop.graph_error
     assert loop.generate_device_window(prompt, 8).tokens == want
+
+
+def test_prefill_with_fused_row_kernels_matches_the_torch_op_prefill():
+    from gpu.decodev2.prefill import set_fused_rows
+
+    _, state, weights = session(MEDIUM_LLAMA, 0)
+    loop = DecodeV2Loop(state, weights)
+    prompt = list(range(1, 21))
+    try:
+        set_fused_rows(False)
+        want = loop.generate_device_window(prompt, 8).tokens
+        want_v = state.kv.v.clone()
+        want_k = state.kv.k.clone()
+    finally:
+        set_fused_rows(True)
+    got = loop.generate_device_window(prompt, 8).tokens
+    assert got == want
+    assert torch.equal(state.kv.v[0], want_v[0]) and torch.equal(state.kv.k[0], want_k[0])
+    # deeper layers see RMSNorm rounded by the decode formula instead of torch's: close, not equal
+    assert (state.kv.k.float() - want_k.float()).abs().max() <= 0.05 * want_k.float().abs().max()

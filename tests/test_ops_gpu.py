@@ -447,3 +447,41 @@ def test_nan_does_not_bleed_across_rows():
     xt, _ = bf16_vec(np.random.default_rng(0), k)
     y = nf4_gemv(pt, st, xt, m, k, k).view(-1).float()
     assert torch.isnan(y[7]) and torch.isfinite(torch.cat([y[:7], y[8:]])).all()
+
+
+def test_prefill_row_kernels_match_the_torch_ops_bit_for_bit():
+    import torch.nn.functional as F
+
+    from gpu.decodev2.rope import apply_rope_torch, rope_tables_torch
+    from gpu.nf4 import nf4_rms, nf4_rms_rows, nf4_rope_kv_rows, nf4_silu_mul
+
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    n, n_q, n_kv, hd, max_seq, start = 37, 8, 2, 64, 96, 11
+    wide = torch.randn((n, (n_q + 2 * n_kv) * hd + 8), generator=gen, device="cuda").to(torch.bfloat16)
+    q, k, v = wide[:, : n_q * hd], wide[:, n_q * hd:(n_q + n_kv) * hd], wide[:, (n_q + n_kv) * hd:-8]
+    cos, sin = rope_tables_torch(max_seq, hd, 10000.0, device="cuda", dtype=torch.bfloat16)
+    k_cache = torch.zeros((max_seq, n_kv, hd), dtype=torch.bfloat16, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    q_out = nf4_rope_kv_rows(q, k, v, k_cache, v_cache, cos, sin, start, n_q, n_kv, hd)
+    c, s_ = cos[start:start + n], sin[start:start + n]
+    assert torch.equal(q_out, apply_rope_torch(q.reshape(n, n_q, hd), c, s_))
+    assert torch.equal(k_cache[start:start + n], apply_rope_torch(k.reshape(n, n_kv, hd), c, s_))
+    assert torch.equal(v_cache[start:start + n], v.reshape(n, n_kv, hd))
+    assert not k_cache[:start].any() and not k_cache[start + n:].any()
+    with pytest.raises(RuntimeError):
+        nf4_rope_kv_rows(q, k, v, k_cache, v_cache, cos, sin, max_seq - 3, n_q, n_kv, hd)
+
+    inter = 176
+    gu = (torch.randn((n, 2 * inter), generator=gen, device="cuda") * 3).to(torch.bfloat16)
+    assert torch.equal(nf4_silu_mul(gu, inter), F.silu(gu[:, :inter]) * gu[:, inter:])
+
+    kdim = 520
+    x = torch.randn((n, kdim + 8), generator=gen, device="cuda").to(torch.bfloat16)[:, :kdim]
+    w = torch.randn(kdim, generator=gen, device="cuda").to(torch.bfloat16)
+    y = nf4_rms_rows(x, w, 1e-6)
+    for r in (0, 5, n - 1):
+        row = torch.empty(kdim, dtype=torch.bfloat16, device="cuda")
+        nf4_rms(x[r].contiguous(), w, row, 1e-6)
+        assert torch.equal(y[r], row)
+    ref = F.rms_norm(x.float(), (kdim,), w.float(), 1e-6)
+    assert (y.float() - ref).abs().max() <= 2 ** -7 * ref.abs().max()
