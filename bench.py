@@ -219,11 +219,11 @@ def run_ours(args, spec) -> None:
     state = loop.state
 
     # prefill (timed apart), leaves next_token ready; one untimed pass first so that
-    # lazily loaded kernels and torch's attention setup are not in the timed window. On one
-    # GPU that pass also captures the chunk, and the timed pass replays it (a prompt shape
-    # that comes back); --eager-prefill times the Python-issued chunk instead.
+    # lazily loaded kernels and torch's attention setup are not in the timed window. That
+    # pass also captures the chunk, and the timed pass replays it (a prompt shape that comes
+    # back); --eager-prefill times the Python-issued chunk instead.
     prefill_mode = "eager"
-    if world == 1 and not args.eager_prefill:
+    if not args.eager_prefill:
         loop.enable_prefill_graphs()
         prefill_mode = "captured chunk graph, replayed"
     loop.reset()

@@ -23,12 +23,13 @@ class PrefillGraphs:
     whole chunk replays as one graph instead. The first time a shape is seen it runs
     eagerly (which also warms every kernel) and is then captured for the next time;
     the token ids live in a static device buffer the replay reads. At most
-    ``max_entries`` shapes are kept (least recently used goes first). Single GPU only.
+    ``max_entries`` shapes are kept (least recently used goes first). Under tensor
+    parallelism the chunk's NCCL all-reduces are captured with it, so every rank must see
+    the same sequence of prompt shapes, and the graphs have to be dropped before the
+    process group is destroyed (``Comm.shutdown`` does).
     """
 
     def __init__(self, state: DecodeState, weights: DeviceWeights, max_entries: int = 4) -> None:
-        if state.spec.tp != 1:
-            raise RuntimeError("prefill graphs are single-GPU")
         self.state, self.weights, self.max_entries = state, weights, int(max_entries)
         self._cache: dict = {}
         self.replays = 0

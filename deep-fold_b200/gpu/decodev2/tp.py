@@ -65,6 +65,8 @@ class Comm:
             if hasattr(h, "_graph"):
                 h._graph = None
                 h.graph_mode = "off"
+            if hasattr(h, "_prefill_graphs"):
+                h._prefill_graphs = None
         gc.collect()
         if torch.cuda.is_available():
             torch.cuda.synchronize()
@@ -256,12 +258,16 @@ def shard_weights(weights: DeviceWeights, rank: int, world: int) -> DeviceWeight
             q = shard_linear_cols(ly.q, rank, world)
             lo, hi = kv_head_rows(full, rank, world)
             k, v = _rows(ly.k, lo, hi), _rows(ly.v, lo, hi)
-        layers.append(DeviceLayer(
+        layer = DeviceLayer(
             ly.norm1, ly.norm2, q, k, v, wqkv,
             shard_linear_rows(ly.o, rank, world),
             _rows(ly.gate, *mlp),
             _rows(ly.up, *mlp),
             shard_linear_rows(ly.down, rank, world, mlp),
-        ))
+        )
+        # on the device the shard's q/k/v and gate/up rows are copied next to each other
+        # (the prefill then runs each group as one GEMM, and the shard no longer keeps
+        # the full matrices alive through its views)
+        layers.append(layer.adjoin() if ly.o.packed.is_cuda else layer)
     return DeviceWeights(local, weights.embed, weights.final_norm,
                          shard_linear_cols(weights.lm_head, rank, world), layers)
