@@ -191,3 +191,26 @@ def test_single_rank_comm_is_a_no_op():
     out = torch.zeros(4)
     comm.all_gather_into(out, t)
     assert torch.equal(out, t)
+
+
+def test_adjoin_rows_stacks_matrices_and_turns_the_handles_into_views():
+    from gpu.decodev2.linear import adjoin_rows
+
+    model = build(MEDIUM_LLAMA, 0)
+    ly = model.layers[0]
+    q, k, v = cpu_linear(ly.q), cpu_linear(ly.k), cpu_linear(ly.v)
+    q.bias = torch.arange(q.M, dtype=torch.float32).to(torch.bfloat16)
+    want = [deq(m) for m in (q, k, v)]
+    stacked = adjoin_rows([q, k, v])
+    assert stacked.M == q.M + k.M + v.M and stacked.K == q.K
+    assert np.array_equal(deq(stacked), np.concatenate(want))
+    # the handles now alias the blob, in order, without a second copy
+    assert q.packed.data_ptr() == stacked.packed.data_ptr()
+    assert k.packed.data_ptr() == stacked.packed.data_ptr() + q.M * (q.K_pad // 2)
+    assert v.scale.data_ptr() == stacked.scale.data_ptr() + (q.M + k.M) * (q.K_pad // 64) * 2
+    for m, w in zip((q, k, v), want):
+        assert m.packed.is_contiguous() and np.array_equal(deq(m), w)
+    assert stacked.bias is not None and stacked.bias.numel() == stacked.M
+    assert torch.equal(stacked.bias[: q.M], q.bias) and not stacked.bias[q.M:].any()
+    with pytest.raises(ValueError):
+        adjoin_rows([cpu_linear(ly.q), cpu_linear(ly.down)])
