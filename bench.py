@@ -109,7 +109,8 @@ def run_reference(args, spec) -> None:
         "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / best["value"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": workload_config(spec, args),
+        "data": "synthetic",
+        "config": dict(workload_config(spec, args), row_split_exchange="none", prefill="not timed"),
         "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
