@@ -260,6 +260,20 @@ extern "C" int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y,
   return launch<0>(a, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu, int32_t out[6]) {
+  if (out == nullptr) return kNull;
+  if (n_rows < 1 || K_pad < kGroup || (K_pad % kGroup) != 0) return kDims;
+  const GemvShape sh = pick_gemv_shape(n_rows, K_pad, swiglu != 0, sm_count());
+  if (sh.R == 0) return kDims;
+  out[0] = sh.R;
+  out[1] = sh.C;
+  out[2] = sh.S;
+  out[3] = sh.G;
+  out[4] = sh.n_tiles;
+  out[5] = sh.grid;
+  return kOk;
+}
+
 extern "C" int chr_nf4_gemv_allreduce(const chr_nf4_dev_t *w, const void *x, void *y,
                                       const chr_nf4_peers_t *peers, const void *add,
                                       void *stream) {

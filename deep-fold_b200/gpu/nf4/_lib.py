@@ -95,6 +95,7 @@ SIGNATURES = {
     "chr_nf4_set_tuning": (None, [c_int32, c_int32, c_int32]),
     "chr_nf4_gemv": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
     "chr_nf4_gemv_f32": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
+    "chr_nf4_gemv_shape": (c_int, [c_int32, c_int32, c_int32, POINTER(c_int32)]),
     "chr_nf4_gemv_allreduce": (
         c_int, [_DEV, c_void_p, c_void_p, POINTER(ChrNf4Peers), c_void_p, c_void_p]
     ),

@@ -138,6 +138,13 @@ const char *chr_nf4_version(void);
 int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y, void *stream,
                      const void *add, const void *rms_w, float rms_eps);
 
+/* Work split the GEMV family uses for a matrix of n_rows x K_pad (swiglu != 0: the
+ * gate/up pair): out = {R rows per warp, C 1024-wide chunks per warp, S K slices,
+ * G row groups per CTA, tiles, CTAs}. Host-only (no launch); -3 when K_pad is beyond
+ * what the kernels cover. Ranks of a tensor-parallel group that pass the same
+ * arguments get the same split, which chr_nf4_gemv_allreduce relies on. */
+int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu, int32_t out[6]);
+
 /* Row-split linear of a tensor-parallel shard with the exchange fused in: ONE
  * launch per rank computes this rank's FP32 partial W_shard . x_shard, pushes its
  * rows into every peer's receive buffer over NVLink (plain peer stores), raises a

@@ -214,3 +214,41 @@ def test_adjoin_rows_stacks_matrices_and_turns_the_handles_into_views():
     assert torch.equal(stacked.bias[: q.M], q.bias) and not stacked.bias[q.M:].any()
     with pytest.raises(ValueError):
         adjoin_rows([cpu_linear(ly.q), cpu_linear(ly.down)])
+
+
+def _gemv_shape(n_rows: int, k_pad: int, swiglu: bool = False):
+    import ctypes
+
+    from gpu.nf4 import _lib
+
+    out = (ctypes.c_int32 * 6)()
+    rc = _lib.load().chr_nf4_gemv_shape(n_rows, k_pad, int(swiglu), out)
+    return rc, tuple(out)
+
+
+@pytest.mark.parametrize("spec", [QWEN25_3B, QWEN25_14B, INTERNLM25_20B, QWEN25_32B])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_gemv_work_split_is_valid_and_agreed_between_ranks(spec, world):
+    """The fused exchange needs every rank to tile a row-split matrix alike: with the widest
+    share's K_pad as the hint they do, and the split stays inside the kernels' limits."""
+    if world > 1:
+        try:
+            shard_spec(spec, world)
+        except ValueError:
+            pytest.skip("this architecture does not shard that way")
+    q_dim = spec.n_q * spec.head_dim
+    for full_k in (q_dim, spec.intermediate):
+        shares = [group_range(full_k, world, r) for r in range(world)] if world > 1 else [(0, full_k)]
+        widest = max(hi - lo for lo, hi in shares)
+        rc, hinted = _gemv_shape(spec.hidden, widest)
+        assert rc == 0
+        r_, c_, s_, g_, tiles, grid = hinted
+        assert r_ in (1, 2, 4) and c_ in (1, 2) and 1 <= s_ * g_ <= 16
+        assert tiles == -(-spec.hidden // (g_ * r_)) and 1 <= grid <= 256
+        assert s_ * c_ * 1024 >= widest          # the slices cover the longest share ...
+        for lo, hi in shares:                    # ... hence every share
+            assert hi - lo <= s_ * c_ * 1024 and (hi - lo) % 64 == 0
+    rc, sw = _gemv_shape(spec.intermediate // world, 64 * -(-spec.hidden // 64), swiglu=True)
+    assert rc == 0 and sw[0] * 2 * sw[1] <= 4    # gate + up rows per warp keep to four loads per buffer
+    assert _gemv_shape(128, 64 * 600)[0] == -3   # K beyond sixteen slices of 2048
+    assert _gemv_shape(0, 64)[0] == -3
