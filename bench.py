@@ -224,7 +224,9 @@ def run_ours(args, spec) -> None:
     # pass also captures the chunk, and the timed pass replays it (a prompt shape that comes
     # back); --eager-prefill times the Python-issued chunk instead.
     prefill_mode = "eager"
-    if not args.eager_prefill:
+    # measured with the chunk graph at 1 and 2 GPUs; wider groups keep the eager chunk
+    # (their NCCL all-reduces inside a captured chunk have not been run on this pool)
+    if not args.eager_prefill and (world <= 2 or args.prefill_graphs):
         loop.enable_prefill_graphs()
         prefill_mode = "captured chunk graph, replayed"
     loop.reset()
@@ -388,6 +390,8 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--eager-prefill", action="store_true",
                     help="time the prefill as issued from Python instead of as a replayed chunk graph")
+    ap.add_argument("--prefill-graphs", action="store_true",
+                    help="replay the prefill chunk as a graph at more than 2 GPUs as well")
     ap.add_argument("--nccl", action="store_true",
                     help="N > 1: sum the row-split partials with NCCL all-reduce launches instead of "
                          "inside the GEMV launch over peer memory")
