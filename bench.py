@@ -1,17 +1,23 @@
 """Benchmark of the NF4 decode/prefill path: batch-1 greedy decode tokens/s.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--model qwen2.5-3b-arch] [--prompt 512]
+                    [--model qwen2.5-32b-arch] [--prompt 1792] [--chunk 512] [--batch B]
 
 One JSON line on stdout. A "step" is one greedy decode token (one replay of the
-captured step graph) of the named random-init architecture after a 512-token
-prompt. ``value`` is the device-window rate (tokens resident, no host traffic),
-``e2e`` the rate with a pinned-host token id copied in and the picked id read
-back every step. ``roofline`` times the dominant kernel (fused SwiGLU GEMV over
-the layers' gate/up matrices, far larger than L2 in total) with CUDA events in
-this same process; ``cpu_baseline`` times the CPU oracle (numpy dequant + float32
-matmul, the reference's CPU NF4 path restated) on a bounded sample.
-``--impl reference`` runs only that CPU path and prints its line.
+captured step graph) of the named random-init architecture after a prompt that
+fills the context (default: the Qwen2.5-32B architecture, 1792-token prompt, so
+the 128 timed steps run against a ~2k-token KV cache). ``value`` is the
+device-window rate (tokens resident, no host traffic), ``e2e`` the rate with a
+pinned-host token id copied in and the picked id read back every step.
+``roofline`` times the dominant kernel (fused SwiGLU GEMV over the layers'
+gate/up matrices, far larger than L2 in total) with CUDA events in this same
+process; ``gemm_roofline`` does the same for the prefill GEMM (stacked gate/up at
+one prompt chunk); ``cpu_baseline`` times the CPU oracle (numpy dequant + float32
+matmul, the reference's CPU NF4 path restated) on the 4096 x 4096 layer at N = 1
+and N = 32, dequant and matmul apart, median of 5. ``--impl reference`` runs only
+the CPU path: each step is a bounded sample (a slab of one gate matrix) that is
+really timed, and the tokens/s it prints is that time scaled by the model's
+weight count.
 """
 
 from __future__ import annotations
@@ -33,86 +39,139 @@ for _p in (str(ROOT / "deep-fold_b200"), str(ROOT / "oracle")):
 METRIC = "decode_tok_s_bs1"
 UNIT = "tok/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the timed kernel, from
-# the ncu capture summarised under profiles/ (SwiGLU GEMV, gate/up [M, K]); other
-# shapes scale by their algorithmic bytes (traffic / algorithmic = 1.001 there).
-NCU_TRAFFIC_RATIO = 24002560 / 23979520
+FALLBACK_TFLOPS = 1590.0
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of one launch
+# of the timed SwiGLU GEMV, from the ncu capture summarised under profiles/.
+NCU_TRAFFIC_RATIO = 1.001
 
 
-def measured_peaks() -> tuple[float, str]:
+def measured_peaks() -> dict:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.is_file():
         try:
-            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+            d = json.loads(path.read_text())
+            return {"hbm": float(d["hbm_gbs"]), "tf_burst": float(d["bf16_tflops"]),
+                    "tf_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    "kind": "measured"}
         except (KeyError, ValueError):
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return {"hbm": FALLBACK_HBM_GBS, "tf_burst": FALLBACK_TFLOPS, "tf_sustained": 1400.0,
+            "kind": "fallback"}
+
+
+def blas_threads() -> int:
+    try:
+        import threadpoolctl
+
+        return max((d.get("num_threads", 1) for d in threadpoolctl.threadpool_info()), default=1)
+    except Exception:  # noqa: BLE001
+        return os.cpu_count() or 1
 
 
 # --------------------------------------------------------------------------- #
-# CPU reference arm: numpy dequant + float32 matmul on a bounded sample
+# CPU legs: numpy dequant + float32 matmul (the reference's CPU NF4 path restated)
 # --------------------------------------------------------------------------- #
-def cpu_layer_sample(spec, repeats: int = 1, seed: int = 0) -> dict:
-    """Time one decoder layer's linears (N=1) and extrapolate to a token.
-
-    The sample is one layer (q,k,v | wqkv, o, gate, up, down) of the named
-    architecture on random NF4 blobs; lm_head is charged by its byte share.
-    """
+def cpu_config1(repeats: int = 5) -> dict:
+    """The 4096 x 4096 layer at N = 1 and N = 32: dequantize and matmul timed apart,
+    median of ``repeats`` (protocol of the reference's CPU oracle, gpu/tests/nf4_oracle.py:119-142)."""
     import numpy as np
 
     import nf4_ref as o
 
-    shapes = spec.linear_shapes()
-    rng = np.random.default_rng(seed)
-    mats = {}
-    for name, (m, k) in shapes.items():
-        if name == "lm_head":
-            continue
-        p, s = o.random_blobs(m, k, seed + len(mats), pad_garbage=False)
-        mats[name] = (p, s, m, k, rng.standard_normal((k, 1)).astype(np.float32))
-    best = float("inf")
-    for _ in range(max(1, repeats)):
+    m = k = 4096
+    p, s = o.random_blobs(m, k, 0, pad_garbage=False)
+    rng = np.random.default_rng(1)
+    out = {"shape": [m, k], "cpu_count": os.cpu_count(), "blas_threads": blas_threads()}
+    med = lambda xs: sorted(xs)[len(xs) // 2]
+    t_deq = []
+    for _ in range(repeats):
         t0 = time.perf_counter()
-        for p, s, m, k, x in mats.values():
-            o.matmul(o.dequantize(p, s, m, k), x)
-        best = min(best, time.perf_counter() - t0)
-    layer_weights = sum(m * k for name, (m, k) in shapes.items() if name != "lm_head")
-    head_weights = shapes["lm_head"][0] * shapes["lm_head"][1]
-    token_s = best * (spec.n_layers + head_weights / layer_weights)
-    try:
-        import threadpoolctl
+        w = o.dequantize(p, s, m, k)
+        t_deq.append(time.perf_counter() - t0)
+    out["dequant_ms"] = med(t_deq) * 1e3
+    for n in (1, 32):
+        x = rng.standard_normal((k, n)).astype(np.float32)
+        t_mm = []
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            o.matmul(w, x)
+            t_mm.append(time.perf_counter() - t0)
+        out[f"matmul_n{n}_ms"] = med(t_mm) * 1e3
+    return out
 
-        blas = max((d.get("num_threads", 1) for d in threadpoolctl.threadpool_info()), default=1)
-    except Exception:  # noqa: BLE001
-        blas = os.cpu_count() or 1
+
+def cpu_sample(spec, rows: int = 8192, seed: int = 0):
+    """One bounded sample of the decode workload on the CPU: the first ``rows`` rows of a
+    gate matrix ([rows, hidden]) dequantized and multiplied with one activation vector.
+    Returns a closure that runs it and the number of weights it covers."""
+    import numpy as np
+
+    import nf4_ref as o
+
+    m, k = min(rows, spec.intermediate), spec.hidden
+    p, s = o.random_blobs(m, k, seed, pad_garbage=False)
+    x = np.random.default_rng(seed).standard_normal((k, 1)).astype(np.float32)
+
+    def run() -> float:
+        t0 = time.perf_counter()
+        o.matmul(o.dequantize(p, s, m, k), x)
+        return time.perf_counter() - t0
+
+    return run, m * k
+
+
+def model_weights(spec) -> int:
+    shapes = spec.linear_shapes()
+    layer = sum(m * k for name, (m, k) in shapes.items() if name != "lm_head")
+    return spec.n_layers * layer + shapes["lm_head"][0] * shapes["lm_head"][1]
+
+
+def cpu_baseline(spec, samples: int = 5) -> dict:
+    run, n_weights = cpu_sample(spec)
+    run()
+    times = sorted(run() for _ in range(samples))
+    med = times[len(times) // 2]
+    token_s = med * model_weights(spec) / n_weights
     return {
-        "value": 1.0 / token_s,
-        "unit": UNIT,
-        "cores": int(blas),
-        "kind": "port",
-        "sample": f"one {spec.name} decoder layer (dequant + f32 matmul, N=1) timed {best * 1e3:.0f} ms, "
-                  f"x{spec.n_layers} layers + lm_head by weight share; host has {os.cpu_count()} cpus",
-        "layer_ms": best * 1e3,
+        "value": 1.0 / token_s, "unit": UNIT, "cores": int(blas_threads()), "kind": "port",
+        "sample": f"{n_weights / 1e6:.0f} M weights of a {spec.name} gate matrix (numpy dequant + f32 "
+                  f"matmul, N=1), median of {samples}: {med * 1e3:.0f} ms, scaled by the model's "
+                  f"{model_weights(spec) / 1e9:.2f} G weights; host has {os.cpu_count()} cpus",
+        "sample_ms": med * 1e3,
+        "config1": cpu_config1(),
     }
 
 
 def run_reference(args, spec) -> None:
+    """The CPU arm: every step is one really timed sample; value scales it to a token."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    for _ in range(max(0, args.warmup)):
-        cpu_layer_sample(spec)
-    times = [cpu_layer_sample(spec) for _ in range(max(1, args.steps))]
-    best = max(times, key=lambda d: d["value"])
+    run, n_weights = cpu_sample(spec)
+    for _ in range(max(1, args.warmup)):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(max(1, args.steps)):
+        run()
+    per_sample = (time.perf_counter() - t0) / max(1, args.steps)
+    token_s = per_sample * model_weights(spec) / n_weights
+    value = 1.0 / token_s
     line = {
         "impl": "reference",
-        "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / best["value"],
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_sample * 1e3,
+        "step_is": "one bounded sample, not one token (see cpu_baseline.sample)",
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": dict(workload_config(spec, args), row_split_exchange="none", prefill="not timed"),
-        "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
-        "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": workload_config(spec, args),
+        "cpu_baseline": {
+            "value": value, "unit": UNIT, "cores": int(blas_threads()), "kind": "port",
+            "sample": f"each step: {n_weights / 1e6:.0f} M weights of a {spec.name} gate matrix, numpy "
+                      f"dequant + f32 matmul at N=1 ({per_sample * 1e3:.0f} ms measured); tokens/s = "
+                      f"1 / (that x {model_weights(spec) / n_weights:.0f}, the model's weight count "
+                      f"over the sample's); host has {os.cpu_count()} cpus",
+        },
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
@@ -120,8 +179,10 @@ def run_reference(args, spec) -> None:
 
 def workload_config(spec, args) -> dict:
     return {
-        "workload": f"{spec.name} random-init NF4 g64, batch 1, {args.prompt}-token prompt then greedy decode",
+        "workload": f"{spec.name} random-init NF4 g64, batch {args.batch}, {args.prompt}-token prompt "
+                    f"then greedy decode",
         "prompt_tokens": args.prompt, "max_seq": spec.max_seq, "layers": spec.n_layers,
+        "batch": args.batch,
         "weights_gb_per_token": round(spec.packed_bytes_per_token() / 1e9, 3),
         "l2": "inputs larger than L2 (weights streamed once per token)",
         "parallelism": f"tp{args.gpus}",
@@ -174,6 +235,31 @@ class Clocks:
                 "reasons": reasons, "samples": len(sm)}
 
 
+def graph_timed(fn, reps: int, torch) -> float:
+    """Milliseconds of one call of ``fn`` when captured in a CUDA graph and replayed
+    ``reps`` times back to back (device time, no Python between the launches)."""
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(reps):
+        graph.replay()
+    t1.record()
+    torch.cuda.synchronize()
+    del graph
+    return t0.elapsed_time(t1) / reps
+
+
 # --------------------------------------------------------------------------- #
 # our arm
 # --------------------------------------------------------------------------- #
@@ -181,7 +267,7 @@ def run_ours(args, spec) -> None:
     import torch
 
     from gpu.decodev2 import DecodeV2Loop, DeviceWeights
-    from gpu.nf4 import nf4_swiglu
+    from gpu.nf4 import _lib, nf4_gemm_rows, nf4_swiglu
 
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -190,12 +276,12 @@ def run_ours(args, spec) -> None:
     torch.cuda.set_device(local)
     dist = None
     if world > 1:
-        import torch.distributed as dist
-
         import datetime
 
+        import torch.distributed as dist
+
         dist.init_process_group("nccl", device_id=torch.device("cuda", local),
-                                timeout=datetime.timedelta(seconds=180))
+                                timeout=datetime.timedelta(seconds=300))
     from gpu.decodev2 import Comm, shard_weights
 
     # every rank draws the same full model (seeded device RNG) and keeps its shard
@@ -205,6 +291,8 @@ def run_ours(args, spec) -> None:
         weights = shard_weights(weights, rank, world)
         torch.cuda.empty_cache()
     spec = weights.spec
+    if args.batch != 1:
+        raise SystemExit("--batch > 1 is not available in this build")
     loop = DecodeV2Loop.from_weights(weights, comm=comm)
     exchange = "none"
     if comm is not None:
@@ -212,7 +300,6 @@ def run_ours(args, spec) -> None:
     gen = torch.Generator().manual_seed(2)
     prompt = torch.randint(0, spec.vocab, (args.prompt,), generator=gen).tolist()
     loop.warmup(prompt=8, tokens=4)
-    fused_why = loop.enable_fused_step() if args.fused else "default"
     mode = loop.capture_graphs()
     if mode != "decodev2":
         raise SystemExit(f"graph capture failed: {loop.graph_error}")
@@ -220,22 +307,19 @@ def run_ours(args, spec) -> None:
     state = loop.state
 
     # prefill (timed apart), leaves next_token ready; one untimed pass first so that
-    # lazily loaded kernels and torch's attention setup are not in the timed window. That
-    # pass also captures the chunk, and the timed pass replays it (a prompt shape that comes
-    # back); --eager-prefill times the Python-issued chunk instead.
-    prefill_mode = "eager"
-    # measured with the chunk graph at 1 and 2 GPUs; wider groups keep the eager chunk
-    # (their NCCL all-reduces inside a captured chunk have not been run on this pool)
-    if not args.eager_prefill and (world <= 2 or args.prefill_graphs):
+    # lazily loaded kernels are not in the timed window. Issued from Python at every N
+    # unless --prefill-graphs asks for the captured chunk.
+    prefill_mode = f"eager, chunks of {args.chunk}"
+    if args.prefill_graphs:
         loop.enable_prefill_graphs()
-        prefill_mode = "captured chunk graph, replayed"
+        prefill_mode = f"captured chunk graphs, replayed, chunks of {args.chunk}"
     loop.reset()
-    loop.prefill_from(prompt, 0)
+    loop.prefill_from(prompt, 0, chunk=args.chunk)
     loop.reset()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     torch.cuda.synchronize()
     ev[0].record()
-    loop.prefill_from(prompt, 0)
+    loop.prefill_from(prompt, 0, chunk=args.chunk)
     ev[1].record()
     torch.cuda.synchronize()
     prefill_ms = ev[0].elapsed_time(ev[1])
@@ -245,6 +329,35 @@ def run_ours(args, spec) -> None:
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def check_status(where: str) -> None:
+        st = _lib.load().chr_nf4_gemv_status()
+        if st != 0:
+            raise SystemExit(f"{where}: GEMV status {st}")
+        if state.peers is not None and state.peers.timed_out():
+            raise SystemExit(f"{where}: a wait for a peer GPU ran out; the sums are not trustworthy")
+
+    # the first ids of the run, read once: the same at every N when tensor parallelism
+    # is correct (and the same on every rank)
+    head_n = min(16, args.steps)
+    head = torch.zeros(head_n, dtype=torch.int64, device=f"cuda:{local}")
+    snap = {"token": state.token.clone(), "position": state.position.clone(),
+            "valid_len": state.valid_len.clone()}
+    for i in range(head_n):
+        step(state, weights)
+        head[i].copy_(state.token.view(-1)[0])
+    torch.cuda.synchronize()
+    greedy_head = [int(t) for t in head.tolist()]
+    if dist is not None:
+        gathered = [torch.zeros_like(head) for _ in range(world)]
+        dist.all_gather(gathered, head)
+        for r, other in enumerate(gathered):
+            if [int(t) for t in other.tolist()] != greedy_head:
+                raise SystemExit(f"rank {r} decoded different ids than rank {rank}")
+    check_status("after the first ids")
+    state.token.copy_(snap["token"])
+    state.position.copy_(snap["position"])
+    state.valid_len.copy_(snap["valid_len"])
 
     # device window: K steps back to back
     for _ in range(args.warmup):
@@ -259,11 +372,14 @@ def run_ours(args, spec) -> None:
     t1.record()
     barrier()
     dev_ms = t0.elapsed_time(t1)
+    check_status("after the device window")
 
     # end to end: pinned host token in, picked id out, every step
-    host_tok = torch.zeros((), dtype=torch.int64).pin_memory()
+    host_tok = torch.zeros(state.token.shape, dtype=torch.int64).pin_memory()
     host_tok.copy_(state.token)
     stream = torch.cuda.current_stream()
+    state.position.copy_(snap["position"])
+    state.valid_len.copy_(snap["valid_len"])
     for _ in range(args.warmup):
         state.token.copy_(host_tok, non_blocking=True)
         step(state, weights)
@@ -281,13 +397,15 @@ def run_ours(args, spec) -> None:
     barrier()
     e2e_ms = max(t0.elapsed_time(t1), (time.perf_counter() - w0) * 1e3)
     clk = clocks.stop()
+    check_status("after the end-to-end window")
 
     # dominant kernel, timed alone over every layer's gate/up (>> L2 in total)
+    peaks = measured_peaks()
     ar = state.arena
     layers = weights.layers
     g0 = layers[0].gate
     per_launch = 2 * g0.nbytes + g0.K * 2 + g0.M * 2
-    reps = max(3, min(20, args.steps))
+    reps = max(3, min(10, args.steps))
 
     def sweep():
         for ly in layers:
@@ -295,27 +413,31 @@ def run_ours(args, spec) -> None:
             nf4_swiglu(g.packed, g.scale, u.packed, u.scale, ar.x, g.M, g.K, g.K_pad,
                        ar.down_in.view(-1), ly.norm2, spec.rms_eps)
 
-    for _ in range(3):
-        sweep()
-    torch.cuda.synchronize()
-    # captured, so the figure is device time per launch without Python between launches
-    sweep_graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(sweep_graph, stream=side):
-            sweep()
-    torch.cuda.current_stream().wait_stream(side)
-    sweep_graph.replay()
-    torch.cuda.synchronize()
-    t0.record()
-    for _ in range(reps):
-        sweep_graph.replay()
-    t1.record()
-    torch.cuda.synchronize()
-    k_us = t0.elapsed_time(t1) * 1e3 / (reps * len(layers))
-    peak, peak_kind = measured_peaks()
+    k_us = graph_timed(sweep, reps, torch) * 1e3 / len(layers)
     achieved = per_launch / (k_us * 1e-6) / 1e9
+
+    # prefill GEMM: the stacked gate/up matrix of every layer against one prompt chunk
+    gu = [ly.gate_up for ly in layers if ly.gate_up is not None]
+    gemm_roof = None
+    if gu:
+        n_tok = args.chunk
+        xin = torch.randn(n_tok, gu[0].K, device=f"cuda:{local}").to(torch.bfloat16)
+        yout = torch.empty(n_tok, gu[0].M, dtype=torch.bfloat16, device=f"cuda:{local}")
+
+        def gemm_sweep():
+            for m in gu:
+                nf4_gemm_rows(m.packed, m.scale, xin, m.M, m.K, m.K_pad, out=yout)
+
+        g_ms = graph_timed(gemm_sweep, max(2, reps // 2), torch) / len(gu)
+        flops = 2.0 * gu[0].M * gu[0].K * n_tok
+        tf = flops / (g_ms * 1e-3) / 1e12
+        gemm_roof = {"kernel": "gemm_rows_kernel (tcgen05, stacked gate/up)", "bound": "tensor",
+                     "achieved": tf, "peak": peaks["tf_sustained"], "peak_kind": peaks["kind"] +
+                     ", sustained (back-to-back launches inside a long sweep)",
+                     "peak_burst": peaks["tf_burst"], "unit": "TFLOP/s",
+                     "frac": tf / peaks["tf_sustained"], "frac_of_burst": tf / peaks["tf_burst"],
+                     "shape": [gu[0].M, gu[0].K, n_tok], "us_per_launch": g_ms * 1e3, "traffic": None}
+        del xin, yout
 
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local}")
     if dist is not None:
@@ -325,57 +447,45 @@ def run_ours(args, spec) -> None:
         dist.barrier()
     if rank != 0:
         if comm is not None:
-            del step, sweep_graph
+            del step
             comm.shutdown(loop)
         return
-    if loop.fused:
-        launches_per_step = 1  # the whole step is one persistent kernel
-        status = loop._fused.status()
-        if status != 0:
-            raise SystemExit(f"persistent step reported status {status}")
-    else:
-        launches_per_step = 1 + spec.n_layers * 5 + 2
+    launches_per_step = 1 + spec.n_layers * 5 + 2
     step_bytes = full_spec.packed_bytes_per_token()
+    tokens = args.steps * args.batch
     line = {
-        "metric": METRIC, "value": args.steps / (dev_ms / 1e3), "unit": UNIT, "n_gpus": world,
+        "metric": METRIC if args.batch == 1 else f"decode_tok_s_bs{args.batch}",
+        "value": tokens / (dev_ms / 1e3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(full_spec, args),
         "prefill_tok_s": args.prompt / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
         "step_hbm_gbs": step_bytes / (dev_ms / args.steps / 1e3) / 1e9,
-        "step_frac_of_hbm_peak": step_bytes / (dev_ms / args.steps / 1e3) / 1e9 / peak,
-        "e2e": {"value": args.steps / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": 8,
-                "d2h_bytes_per_step": 8},
+        "step_frac_of_hbm_peak": step_bytes / (dev_ms / args.steps / 1e3) / 1e9 / peaks["hbm"],
+        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT,
+                "h2d_bytes_per_step": 8 * args.batch, "d2h_bytes_per_step": 8 * args.batch},
         "gpu_launches": launches_per_step * args.steps,
+        "greedy_ids_head": greedy_head,
         "clocks": clk,
     }
-    gemv_roof = {"kernel": "nf4_gemv_kernel<swiglu> (gate+up, fused RMSNorm)", "bound": "hbm",
-                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                 "frac": achieved / peak, "bytes_per_launch": per_launch, "us_per_launch": k_us,
-                 "traffic": int(round(per_launch * NCU_TRAFFIC_RATIO)),
-                 "traffic_source": "ncu capture of the 3B gate/up launch (24,002,560 B), scaled by "
-                                   "algorithmic bytes for other shapes"}
-    if loop.fused:
-        # one launch = one token: every packed weight byte and scale is read once
-        step_us = dev_ms / args.steps * 1e3
-        line["roofline"] = {"kernel": "decode_step_kernel (whole greedy step, persistent)",
-                            "bound": "hbm", "achieved": step_bytes / (step_us * 1e-6) / 1e9,
-                            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                            "frac": step_bytes / (step_us * 1e-6) / 1e9 / peak,
-                            "bytes_per_launch": step_bytes, "us_per_launch": step_us,
-                            "traffic": None}
-        line["gemv_alone"] = gemv_roof
-    else:
-        line["roofline"] = gemv_roof
-        line["step_mode"] = f"launch chain ({fused_why})"
-    line["config"]["row_split_exchange"] = exchange
-    line["config"]["prefill"] = prefill_mode
+    line["roofline"] = {"kernel": "nf4_gemv_kernel<swiglu> (gate+up, fused RMSNorm)", "bound": "hbm",
+                        "achieved": achieved, "peak": peaks["hbm"], "peak_kind": peaks["kind"],
+                        "unit": "GB/s", "frac": achieved / peaks["hbm"],
+                        "frac_of_nominal_8tbs": achieved / 8000.0,
+                        "bytes_per_launch": per_launch, "us_per_launch": k_us,
+                        "traffic": int(round(per_launch * NCU_TRAFFIC_RATIO)),
+                        "traffic_source": "ncu capture of one gate/up launch (profiles/), scaled by "
+                                          "algorithmic bytes"}
+    if gemm_roof is not None:
+        line["gemm_roofline"] = gemm_roof
+    line["step_mode"] = "launch chain in one CUDA graph"
+    line["row_split_exchange"] = exchange
+    line["prefill_mode"] = prefill_mode
     if not args.no_cpu:
-        cb = cpu_layer_sample(full_spec)
-        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        line["cpu_baseline"] = cpu_baseline(full_spec)
     print(json.dumps(line), flush=True)
     if comm is not None:
-        del step, sweep_graph
+        del step
         comm.shutdown(loop)
 
 
@@ -385,24 +495,26 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    ap.add_argument("--model", default="qwen2.5-3b-arch")
-    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--model", default="qwen2.5-32b-arch")
+    ap.add_argument("--prompt", type=int, default=None,
+                    help="prompt tokens (default: fills the context up to the timed steps)")
+    ap.add_argument("--chunk", type=int, default=512, help="prefill chunk width")
+    ap.add_argument("--batch", type=int, default=1, help="sequences decoded together")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--eager-prefill", action="store_true",
-                    help="time the prefill as issued from Python instead of as a replayed chunk graph")
     ap.add_argument("--prefill-graphs", action="store_true",
-                    help="replay the prefill chunk as a graph at more than 2 GPUs as well")
+                    help="replay the prefill chunks as captured graphs instead of issuing them from Python")
     ap.add_argument("--nccl", action="store_true",
                     help="N > 1: sum the row-split partials with NCCL all-reduce launches instead of "
                          "inside the GEMV launch over peer memory")
-    ap.add_argument("--fused", action="store_true",
-                    help="run the step as one persistent kernel instead of the graph of one launch "
-                         "per operation (same bits; slower on the 3B shapes as measured)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     from gpu.decodev2.arch import CONFIGS
 
     spec = CONFIGS[args.model]
+    if args.prompt is None:
+        # leave room for the first ids, the warm-up and two timed windows
+        room = 16 + 2 * (args.warmup + args.steps) + 8
+        args.prompt = max(32, min(1792, spec.max_seq - room))
     if args.impl == "reference":
         run_reference(args, spec)
     else:

@@ -8,7 +8,7 @@
 // (kv head, head chunk) to arrive merges the splits.
 #pragma once
 
-#include "gemv_core.cuh"
+#include "nf4_common.cuh"
 
 namespace chr {
 

@@ -23,10 +23,10 @@ OUT_DIR = CSRC.parent / "gpu" / "nf4"
 LIB = OUT_DIR / "libchr_nf4.so"
 OBJ_DIR = CSRC / "build"
 
-CUDA_SOURCES = ("gemv.cu", "decode_ops.cu", "decode_step.cu", "prefill_ops.cu", "gemm.cu", "gemm_tc.cu", "codec_dev.cu",
+CUDA_SOURCES = ("gemv.cu", "decode_ops.cu", "prefill_ops.cu", "gemm.cu", "gemm_tc.cu", "codec_dev.cu",
                 "version.cu")
 CXX_SOURCES = ("codec.cpp",)
-HEADERS = ("nf4_common.cuh", "gemv_core.cuh", "attn_core.cuh", "gemm_plan.h")
+HEADERS = ("nf4_common.cuh", "gemv_ring.cuh", "attn_core.cuh", "gemm_plan.h")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

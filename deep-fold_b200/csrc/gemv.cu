@@ -1,85 +1,123 @@
 // Decode-side NF4 GEMV family for sm_100a: y = dequant(W) . x on CUDA cores, one
-// persistent CTA per SM striding over row tiles. The device core (inner loop, work
-// split, numerics) is in gemv_core.cuh; this file holds the kernels launched per
-// matrix and their C entry points.
+// persistent CTA per SM striding over row tiles that an elected thread streams into
+// a shared-memory ring with bulk copies. The device core (ring, inner loop, work
+// split, numerics) is in gemv_ring.cuh; this file holds the kernels' C entry points.
 
-#include "gemv_core.cuh"
+#include "gemv_ring.cuh"
 
 namespace chr {
+
+// Sticky status word of the GEMV family on this device: 0, or kStGemvWindow /
+// kStGemvTimeout from the kernel that met the problem. Lives in the library, read
+// and cleared through chr_nf4_gemv_status().
+__device__ int g_gemv_status;
+
 namespace {
 
-template <int R, int C, int MODE>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1)
-nf4_gemv_kernel(const GemvArgs a) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  // The next kernel of the chain may start launching; the first tile's weights go
-  // in flight inside gemv_run before the table is built and x is read.
-  pdl_trigger();
-  const uint32_t tab_base = pair_table_base(smem);
-  if (tab_base == 0u) return;  // mis-sized launch: the host entry points never produce one
-  const uint32_t tab_lane = tab_base + static_cast<uint32_t>(threadIdx.x & 31) * 8u;
-  gemv_run<R, C, MODE>(a, reinterpret_cast<float *>(smem),
-                       reinterpret_cast<__nv_bfloat16 *>(smem + kPartBytes), tab_lane, blockIdx.x,
-                       gridDim.x, [&] {
-                         build_pair_table(tab_base, threadIdx.x, blockDim.x);
-                         // x (and the residual / outputs) belong to the previous kernel
-                         // until it completes
-                         pdl_wait();
-                       });
+// Device address of g_gemv_status, looked up once per device (a host-side runtime
+// query, no launch and no allocation). Two host threads racing on the first call
+// both store the same value.
+int *gemv_status_ptr() {
+  static int *ptr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptr[dev] == nullptr) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_gemv_status) != cudaSuccess) return nullptr;
+    ptr[dev] = static_cast<int *>(p);
+  }
+  return ptr[dev];
+}
+
+constexpr int kV = CHR_GEMV_VARIANT;  // the lookup variant this library is built with
+
+bool scales_aligned16(const GemvArgs &a, int n_mats) {
+  for (int i = 0; i < n_mats; ++i) {
+    if (!aligned(a.scale[i], 16)) return false;
+  }
+  return true;
+}
+
+template <int V, int MODE>
+GemvShape shape_for(const GemvArgs &a, int shape_k_pad = 0) {
+  const int n_mats = MODE == 0 ? 1 : (MODE == 1 ? 2 : 3);
+  GemvShape sh = pick_gemv_shape<V>(a.n_rows, a.K, shape_k_pad > 0 ? shape_k_pad : a.K_pad, MODE,
+                                    sm_count(), max_chunks_per_warp<V>(), scales_aligned16(a, n_mats),
+                                    a.rows_end);
+  return sh;
+}
+
+template <int MODE>
+int launch(const GemvArgs &proto, cudaStream_t st) {
+  GemvArgs a = proto;
+  a.status = gemv_status_ptr();
+  if (a.status == nullptr) return kLaunch;
+  const GemvShape sh = shape_for<kV, MODE>(a);
+  if (sh.R == 0) return kDims;  // K beyond what a CTA can stage
+  return launch_gemv<kV, MODE>(a, sh, st);
 }
 
 // ---------------------------------------------------------------------------
 // Row-split GEMV with the cross-GPU sum fused in (see chr_nf4_gemv_allreduce).
 // ---------------------------------------------------------------------------
 constexpr unsigned int kPeerPolls = 1u << 22;
+unsigned int &peer_polls() {
+  static unsigned int v = kPeerPolls;
+  return v;
+}
 
 struct PeerArgs {
   int rank, world;
+  int capacity;  // rows a source rank's slot holds
   float *recv[CHR_NF4_AR_MAX_RANKS];
   unsigned int *flags[CHR_NF4_AR_MAX_RANKS];
   unsigned int *epoch;  // [0] calls completed, [1] exit ticket
   int *status;
+  unsigned int polls;
 };
 
-template <int R, int C>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1)
+template <int V, int R, int C>
+__global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
 nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  const uint32_t tab_base = pair_table_base(smem);
-  if (tab_base == 0u) return;
+  extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x;
-  const uint32_t tab_lane = tab_base + static_cast<uint32_t>(tid & 31) * 8u;
   const int M = a.n_rows;
-  pdl_trigger();  // the next kernel of the chain may build its table meanwhile
+  pdl_trigger();  // the next kernel of the chain may request its tiles meanwhile
 
   // The epoch is read once the previous kernel of the stream has completed (and with
   // it every earlier one): nobody writes the word before every CTA of the previous
   // call has taken its exit ticket, so all CTAs (and, call for call, all ranks) agree.
-  unsigned int e = 0;
-  size_t half = 0;
-  float *mine = nullptr;
+  // (kept in the ring header of the dynamic allocation: the kernels of this family
+  // declare no static shared memory, their layout counts on it)
+  const uint32_t epoch_slot = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + 144u;
   GemvArgs b = a;
-  gemv_run<R, C, 0>(b, reinterpret_cast<float *>(smem),
-                    reinterpret_cast<__nv_bfloat16 *>(smem + kPartBytes), tab_lane, blockIdx.x,
-                    gridDim.x, [&] {
-                      build_pair_table(tab_base, tid, blockDim.x);
-                      pdl_wait();  // x and the residual belong to the previous kernel until it ends
-                      e = *reinterpret_cast<volatile unsigned int *>(pa.epoch) + 1u;
-                      half = static_cast<size_t>(e & 1u) * pa.world * M;
-                      mine = pa.recv[pa.rank] + half + static_cast<size_t>(pa.rank) * M;
-                      b.y32 = mine;  // the partial lands in this rank's own slot first
-                    });
-  __syncthreads();  // this CTA's rows are stored
+  // Every thread passes the same y32: this rank's own slot of the current half.
+  // The half depends on the epoch, which is only known after the dependency wait;
+  // gemv_run reads b.y32 after wait() returns.
+  gemv_run<V, R, C, 0>(b, smem, blockIdx.x, gridDim.x, [&] {
+    pdl_wait();  // x and the residual belong to the previous kernel until it ends
+    const unsigned int e = *reinterpret_cast<volatile unsigned int *>(pa.epoch) + 1u;
+    const size_t half = static_cast<size_t>(e & 1u) * pa.world * pa.capacity;
+    b.y32 = pa.recv[pa.rank] + half + static_cast<size_t>(pa.rank) * pa.capacity;
+    if (tid == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(epoch_slot), "r"(e) : "memory");
+  });
+  __syncthreads();  // this CTA's rows are stored (by its helper warp or its workers)
+  unsigned int e;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(epoch_slot) : "memory");
+  const size_t half = static_cast<size_t>(e & 1u) * pa.world * pa.capacity;
+  float *mine = pa.recv[pa.rank] + half + static_cast<size_t>(pa.rank) * pa.capacity;
 
   // Rows of this CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of G*R rows.
   const int rt = a.G * R;
   // 1. push them into every peer's slot for this rank
   for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
-    const int row = tile * rt + tid;
-    if (tid < rt && row < M) {
-      const float v = __ldcg(mine + row);
-      for (int p = 0; p < pa.world; ++p) {
-        if (p != pa.rank) pa.recv[p][half + static_cast<size_t>(pa.rank) * M + row] = v;
+    for (int u = tid; u < rt; u += blockDim.x) {
+      const int row = tile * rt + u;
+      if (row < M) {
+        const float v = __ldcg(mine + row);
+        for (int p = 0; p < pa.world; ++p) {
+          if (p != pa.rank) pa.recv[p][half + static_cast<size_t>(pa.rank) * pa.capacity + row] = v;
+        }
       }
     }
   }
@@ -107,7 +145,7 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
       asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
       // epochs only grow; the difference form survives the 32-bit wrap
       if (static_cast<int>(seen - e) >= 0) break;
-      if (++polls >= kPeerPolls) {
+      if (++polls >= pa.polls) {
         atomicExch(pa.status, 1);
         break;
       }
@@ -118,14 +156,16 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
   // 3. sum in rank order, add the residual, round once
   __nv_bfloat16 *y = a.y[0];
   for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
-    const int row = tile * rt + tid;
-    if (tid < rt && row < M) {
-      float v = 0.f;
-      for (int r = 0; r < pa.world; ++r) {
-        v += __ldcg(pa.recv[pa.rank] + half + static_cast<size_t>(r) * M + row);
+    for (int u = tid; u < rt; u += blockDim.x) {
+      const int row = tile * rt + u;
+      if (row < M) {
+        float v = 0.f;
+        for (int r = 0; r < pa.world; ++r) {
+          v += __ldcg(pa.recv[pa.rank] + half + static_cast<size_t>(r) * pa.capacity + row);
+        }
+        v += __bfloat162float(y[row]);
+        y[row] = __float2bfloat16(v);
       }
-      v += __bfloat162float(y[row]);
-      y[row] = __float2bfloat16(v);
     }
   }
   // 4. the last CTA out publishes the new epoch
@@ -139,81 +179,59 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
   }
 }
 
-__global__ void smem_offset_probe(int *out) {
-  extern __shared__ __align__(16) unsigned char probe_smem[];
-  if (threadIdx.x == 0) *out = static_cast<int>(__cvta_generic_to_shared(probe_smem));
-}
-
-template <int MODE>
-int launch(const GemvArgs &proto, cudaStream_t st) {
-  constexpr bool swiglu = MODE == 1;
+template <int V>
+int launch_ar(const GemvArgs &proto, const GemvShape &sh, const PeerArgs &pa, cudaStream_t st) {
   GemvArgs a = proto;
-  const GemvShape sh = pick_gemv_shape(a.n_rows, a.K_pad, swiglu, sm_count());
-  if (sh.R == 0) return kDims;  // K beyond 16 slices of 2048 is not supported by this path
-  const int smem_bytes = table_smem_request(((a.K + 7) / 8) * 16);
-  if (smem_bytes == 0) return kDims;  // x does not fit in front of the table
   a.S = sh.S;
   a.G = sh.G;
   a.n_tiles = sh.n_tiles;
+  a.n_slots = sh.n_slots;
+  a.scale_bulk = sh.scale_bulk;
+  a.tail_scale_bulk = sh.tail_scale_bulk;
   const dim3 grid(static_cast<unsigned>(sh.grid));
-  const dim3 block(static_cast<unsigned>(sh.S * sh.G * 32));
-
-#define CHR_LAUNCH(RR, CC)                                                                   \
-  do {                                                                                       \
-    static int attr_bytes = 0;                                                               \
-    if (attr_bytes < smem_bytes) {                                                           \
-      if (cudaFuncSetAttribute(nf4_gemv_kernel<RR, CC, MODE>,                                \
-                               cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
-                               smem_bytes) != cudaSuccess) {                                 \
-        return kLaunch;                                                                      \
-      }                                                                                      \
-      attr_bytes = smem_bytes;                                                               \
-    }                                                                                        \
-    if (launch_chain(nf4_gemv_kernel<RR, CC, MODE>, grid, block, smem_bytes, st, a) !=       \
-        cudaSuccess) {                                                                       \
-      return kLaunch;                                                                        \
-    }                                                                                        \
+  const dim3 block(static_cast<unsigned>((sh.S * sh.G + 1) * 32));
+  const int smem_limit = static_cast<int>(kWindowEnd - kReserved);
+#define CHR_LAUNCH_AR(RR, CC)                                                                  \
+  do {                                                                                         \
+    static int attr_done[64] = {};                                                             \
+    if (!ensure_smem_attr(nf4_gemv_ar_kernel<V, RR, CC>, smem_limit, attr_done)) return kLaunch; \
+    if (launch_chain(nf4_gemv_ar_kernel<V, RR, CC>, grid, block, sh.smem_bytes, st, a, pa) !=   \
+        cudaSuccess) {                                                                         \
+      return kLaunch;                                                                          \
+    }                                                                                          \
+    return kOk;                                                                                \
   } while (0)
-
-  if (sh.C == 2) {
-    if (sh.R == 2) {
-      if constexpr (MODE != 1) CHR_LAUNCH(2, 2); else return kLaunch;
-    } else {
-      CHR_LAUNCH(1, 2);
-    }
-  } else {
-    if (sh.R == 4) {
-      if constexpr (MODE != 1) CHR_LAUNCH(4, 1); else return kLaunch;
-    } else if (sh.R == 2) {
-      CHR_LAUNCH(2, 1);
-    } else {
-      CHR_LAUNCH(1, 1);
-    }
+  switch (sh.C * 8 + sh.R) {
+    case 1 * 8 + 1: CHR_LAUNCH_AR(1, 1);
+    case 1 * 8 + 2: CHR_LAUNCH_AR(2, 1);
+    case 1 * 8 + 4: CHR_LAUNCH_AR(4, 1);
+    case 1 * 8 + 8: CHR_LAUNCH_AR(8, 1);
+    case 2 * 8 + 1: CHR_LAUNCH_AR(1, 2);
+    case 2 * 8 + 2: CHR_LAUNCH_AR(2, 2);
+    case 2 * 8 + 4: CHR_LAUNCH_AR(4, 2);
+    default: break;
   }
-#undef CHR_LAUNCH
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+#undef CHR_LAUNCH_AR
+  return kDims;
+}
+
+GemvArgs one_matrix(const chr_nf4_dev_t *w, const void *x, const void *add, const void *rms_w,
+                    float rms_eps) {
+  GemvArgs a{};
+  a.packed[0] = w->packed;
+  a.scale[0] = w->scale;
+  a.extra[0] = static_cast<const __nv_bfloat16 *>(add);
+  a.rows_end[0] = a.rows_end[1] = a.rows_end[2] = w->M;
+  a.n_rows = w->M;
+  a.K = w->K;
+  a.K_pad = w->K_pad;
+  a.x = static_cast<const __nv_bfloat16 *>(x);
+  a.rms_w = static_cast<const __nv_bfloat16 *>(rms_w);
+  a.rms_eps = rms_eps;
+  return a;
 }
 
 }  // namespace
-
-int smem_window_offset() {
-  static int cached[64];
-  static bool have[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
-  if (have[dev]) return cached[dev];
-  int *d = nullptr;
-  int v = -1;
-  if (cudaMalloc(&d, sizeof(int)) != cudaSuccess) return -1;
-  smem_offset_probe<<<1, 32, 1024>>>(d);
-  const bool ok = cudaMemcpy(&v, d, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess;
-  cudaFree(d);
-  if (!ok || v < 0 || v > 16384) return -1;
-  cached[dev] = v;
-  have[dev] = true;
-  return v;
-}
-
 }  // namespace chr
 
 using namespace chr;
@@ -224,18 +242,8 @@ extern "C" int chr_nf4_gemv(const chr_nf4_dev_t *w, const void *x, void *y, void
   const int rc = check_matrix(w);
   if (rc != kOk) return rc;
   if (!aligned(w->packed, 16) || !aligned(x, 16) || !aligned(w->scale, 2)) return kAlign;
-  GemvArgs a{};
-  a.packed[0] = w->packed;
-  a.scale[0] = w->scale;
+  GemvArgs a = one_matrix(w, x, add, rms_w, rms_eps);
   a.y[0] = static_cast<__nv_bfloat16 *>(y);
-  a.extra[0] = static_cast<const __nv_bfloat16 *>(add);
-  a.rows_end[0] = a.rows_end[1] = a.rows_end[2] = w->M;
-  a.n_rows = w->M;
-  a.K = w->K;
-  a.K_pad = w->K_pad;
-  a.x = static_cast<const __nv_bfloat16 *>(x);
-  a.rms_w = static_cast<const __nv_bfloat16 *>(rms_w);
-  a.rms_eps = rms_eps;
   return launch<0>(a, static_cast<cudaStream_t>(stream));
 }
 
@@ -245,25 +253,22 @@ extern "C" int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y,
   const int rc = check_matrix(w);
   if (rc != kOk) return rc;
   if (!aligned(w->packed, 16) || !aligned(x, 16) || !aligned(w->scale, 2)) return kAlign;
-  GemvArgs a{};
-  a.packed[0] = w->packed;
-  a.scale[0] = w->scale;
+  GemvArgs a = one_matrix(w, x, add, rms_w, rms_eps);
   a.y32 = y;
-  a.extra[0] = static_cast<const __nv_bfloat16 *>(add);
-  a.rows_end[0] = a.rows_end[1] = a.rows_end[2] = w->M;
-  a.n_rows = w->M;
-  a.K = w->K;
-  a.K_pad = w->K_pad;
-  a.x = static_cast<const __nv_bfloat16 *>(x);
-  a.rms_w = static_cast<const __nv_bfloat16 *>(rms_w);
-  a.rms_eps = rms_eps;
   return launch<0>(a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu, int32_t out[6]) {
   if (out == nullptr) return kNull;
   if (n_rows < 1 || K_pad < kGroup || (K_pad % kGroup) != 0) return kDims;
-  const GemvShape sh = pick_gemv_shape(n_rows, K_pad, swiglu != 0, sm_count());
+  GemvArgs a{};
+  a.n_rows = n_rows;
+  a.K = K_pad;
+  a.K_pad = K_pad;
+  a.rows_end[0] = a.rows_end[1] = a.rows_end[2] = n_rows;
+  // alignment of the scale blobs does not change R, C, S, G: report the aligned case
+  const GemvShape sh = pick_gemv_shape<kV>(n_rows, K_pad, K_pad, swiglu != 0 ? 1 : 0, sm_count(),
+                                          max_chunks_per_warp<kV>(), true, a.rows_end);
   if (sh.R == 0) return kDims;
   out[0] = sh.R;
   out[1] = sh.C;
@@ -272,6 +277,21 @@ extern "C" int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu,
   out[4] = sh.n_tiles;
   out[5] = sh.grid;
   return kOk;
+}
+
+extern "C" void chr_nf4_set_peer_polls(uint32_t polls) {
+  peer_polls() = polls == 0 ? kPeerPolls : polls;
+}
+
+extern "C" int chr_nf4_gemv_status(void) {
+  int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return kLaunch;
+  if (cudaMemcpyFromSymbol(&v, g_gemv_status, sizeof(int)) != cudaSuccess) return kLaunch;
+  if (v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gemv_status, &zero, sizeof(int));
+  }
+  return v;
 }
 
 extern "C" int chr_nf4_gemv_allreduce(const chr_nf4_dev_t *w, const void *x, void *y,
@@ -286,9 +306,15 @@ extern "C" int chr_nf4_gemv_allreduce(const chr_nf4_dev_t *w, const void *x, voi
     return kDims;
   }
   if (peers->epoch == nullptr || peers->status == nullptr) return kNull;
+  // The receive buffers hold `capacity` rows per source rank and half; more rows would
+  // run the peer stores into the flag words behind them.
+  if (peers->capacity < 1) return kDims;
+  if (w->M > peers->capacity) return kWorkspace;
   PeerArgs pa{};
   pa.rank = peers->rank;
   pa.world = peers->world;
+  pa.capacity = peers->capacity;
+  pa.polls = peer_polls();
   for (int p = 0; p < peers->world; ++p) {
     if (peers->recv[p] == nullptr || peers->flags[p] == nullptr) return kNull;
     pa.recv[p] = static_cast<float *>(peers->recv[p]);
@@ -297,16 +323,10 @@ extern "C" int chr_nf4_gemv_allreduce(const chr_nf4_dev_t *w, const void *x, voi
   pa.epoch = static_cast<unsigned int *>(peers->epoch);
   pa.status = static_cast<int *>(peers->status);
 
-  GemvArgs a{};
-  a.packed[0] = w->packed;
-  a.scale[0] = w->scale;
+  GemvArgs a = one_matrix(w, x, add, nullptr, 0.f);
   a.y[0] = static_cast<__nv_bfloat16 *>(y);
-  a.extra[0] = static_cast<const __nv_bfloat16 *>(add);
-  a.rows_end[0] = a.rows_end[1] = a.rows_end[2] = w->M;
-  a.n_rows = w->M;
-  a.K = w->K;
-  a.K_pad = w->K_pad;
-  a.x = static_cast<const __nv_bfloat16 *>(x);
+  a.status = gemv_status_ptr();
+  if (a.status == nullptr) return kLaunch;
   // Every rank must tile the rows the same way; with uneven K shares the ranks agree
   // on the shape of the longest share.
   int shape_k_pad = a.K_pad;
@@ -314,41 +334,10 @@ extern "C" int chr_nf4_gemv_allreduce(const chr_nf4_dev_t *w, const void *x, voi
     if (peers->shape_k_pad < a.K_pad || (peers->shape_k_pad % kGroup) != 0) return kDims;
     shape_k_pad = peers->shape_k_pad;
   }
-  const GemvShape sh = pick_gemv_shape(a.n_rows, shape_k_pad, false, sm_count());
-  if (sh.R == 0 || sh.grid > CHR_NF4_AR_MAX_CTAS) return kDims;
-  a.S = sh.S;
-  a.G = sh.G;
-  a.n_tiles = sh.n_tiles;
-  const int smem_bytes = table_smem_request(((a.K + 7) / 8) * 16);
-  if (smem_bytes == 0) return kDims;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const dim3 grid(static_cast<unsigned>(sh.grid));
-  const dim3 block(static_cast<unsigned>(sh.S * sh.G * 32));
-
-#define CHR_LAUNCH_AR(RR, CC)                                                                \
-  do {                                                                                       \
-    static int attr_bytes = 0;                                                               \
-    if (attr_bytes < smem_bytes) {                                                           \
-      if (cudaFuncSetAttribute(nf4_gemv_ar_kernel<RR, CC>,                                   \
-                               cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
-                               smem_bytes) != cudaSuccess) {                                 \
-        return kLaunch;                                                                      \
-      }                                                                                      \
-      attr_bytes = smem_bytes;                                                               \
-    }                                                                                        \
-    if (launch_chain(nf4_gemv_ar_kernel<RR, CC>, grid, block, smem_bytes, st, a, pa) !=      \
-        cudaSuccess) {                                                                       \
-      return kLaunch;                                                                        \
-    }                                                                                        \
-  } while (0)
-
-  if (sh.C == 2) {
-    if (sh.R == 2) CHR_LAUNCH_AR(2, 2); else CHR_LAUNCH_AR(1, 2);
-  } else {
-    if (sh.R == 4) CHR_LAUNCH_AR(4, 1); else if (sh.R == 2) CHR_LAUNCH_AR(2, 1); else CHR_LAUNCH_AR(1, 1);
-  }
-#undef CHR_LAUNCH_AR
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
+  const GemvShape sh = shape_for<kV, 0>(a, shape_k_pad);
+  if (sh.R == 0 || sh.grid > CHR_NF4_AR_MAX_CTAS) return kDims;
+  return launch_ar<kV>(a, sh, pa, st);
 }
 
 extern "C" int chr_nf4_gemv_qkv(const chr_nf4_dev_t *q, const chr_nf4_dev_t *k,

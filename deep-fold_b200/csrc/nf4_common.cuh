@@ -110,6 +110,15 @@ __device__ __forceinline__ uint16_t ld_stream_u16(const void *p) {
   return v;
 }
 
+// Activation loads go through L2 (ld.global.cg): x, the residual and the RMSNorm
+// input were written by the previous kernel of the chain.
+__device__ __forceinline__ uint4 ld_act16(const void *p) {
+  return __ldcg(reinterpret_cast<const uint4 *>(p));
+}
+__device__ __forceinline__ float ld_act_bf16(const __nv_bfloat16 *p) {
+  return bf16_lo(static_cast<uint32_t>(__ldcg(reinterpret_cast<const unsigned short *>(p))));
+}
+
 // Packed FP32 pairs live in 64-bit registers end to end, so that no pack/unpack
 // moves surround the packed FMA (fma.rn.f32x2, sm_100).
 typedef unsigned long long f32x2_t;

@@ -6,7 +6,6 @@ from .arch import (CONFIGS, INTERNLM25_20B, MEDIUM_LLAMA, QWEN25_3B, QWEN25_14B,
                    TINY_INTERNLM, TINY_LLAMA, ArchSpec, shard_spec, with_max_seq)
 from .chrfile import load_weights, save_synth, tensor_names
 from .embed import PackedEmbed, bind_embed, gather_embed
-from .fused import FusedStep, fused_step_supported
 from .graph import GreedyGraph, capture_greedy
 from .linear import (DeviceLayer, DeviceLinear, DeviceWeights, linear_backend, nf4_linear,
                      set_linear_backend)
@@ -24,8 +23,6 @@ __all__ = [
     "save_synth",
     "tensor_names",
     "PrefillGraphs",
-    "FusedStep",
-    "fused_step_supported",
     "ArchSpec", "Arena", "CONFIGS", "DecodeState", "DecodeV2Loop", "DeviceLayer", "DeviceLinear",
     "DeviceWeights", "Generation", "GraphSafeKV", "GreedyGraph", "INTERNLM25_20B", "MEDIUM_LLAMA",
     "Nf4Matrix", "PackedEmbed", "QWEN25_14B", "QWEN25_32B", "QWEN25_3B", "SynthLayer",

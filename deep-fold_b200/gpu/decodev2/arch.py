@@ -143,6 +143,12 @@ def shard_spec(spec: ArchSpec, world: int, rank: int = 0) -> ArchSpec:
         raise ValueError(f"{spec.name}: n_kv={spec.n_kv} and tp={world} do not nest")
     if (spec.n_q // world) % n_kv:
         raise ValueError("local query heads must be a multiple of local kv heads")
+    # o_proj is cut along K at NF4 group boundaries and q along whole heads: the two
+    # cuts only coincide when a rank's query width is made of whole groups; the MLP
+    # width must be whole groups for its tail not to be dropped.
+    if ((spec.n_q // world) * spec.head_dim) % 64 or spec.intermediate % 64:
+        raise ValueError(f"{spec.name}: per-rank query width and the MLP width must be multiples "
+                         f"of 64 under tp={world}")
     lo, hi = group_range(spec.intermediate, world, rank)
     return replace(spec, n_q=spec.n_q // world, n_kv=n_kv, intermediate=hi - lo,
                    tp=world, kv_replicas=reps)

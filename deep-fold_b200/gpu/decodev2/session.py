@@ -17,7 +17,6 @@ from dataclasses import dataclass, field
 
 import torch
 
-from .fused import FusedStep, fused_step_supported
 from .graph import capture_greedy
 from .linear import DeviceWeights
 from .prefill import prefill_chunk_width
@@ -69,7 +68,6 @@ class DecodeV2Loop:
         self.graph_mode = "off"
         self.graph_error: str | None = None
         self._graph = None
-        self._fused: FusedStep | None = None
         self._prefill_graphs: PrefillGraphs | None = None
 
     @classmethod
@@ -118,30 +116,11 @@ class DecodeV2Loop:
 
     # ------------------------------------------------------------------- decode
     def _step(self):
-        if self._graph is not None:
-            return self._graph
-        return self._fused if self._fused is not None else greedy_decode
-
-    def enable_fused_step(self, on: bool = True) -> str | None:
-        """Run decode steps as one persistent launch instead of one launch per operation
-        (same bits). Returns ``None`` on success, else why the model is not covered;
-        drops a captured graph, so call ``capture_graphs`` afterwards if wanted."""
-        self._graph, self.graph_mode = None, "off"
-        if not on:
-            self._fused = None
-            return None
-        why = fused_step_supported(self.state, self.weights)
-        if why is None:
-            self._fused = FusedStep(self.state, self.weights)
-        return why
+        return self._graph if self._graph is not None else greedy_decode
 
     def enable_prefill_graphs(self, on: bool = True, max_entries: int = 4) -> None:
         """Replay prefill chunks whose (start, length) has been seen before as CUDA graphs."""
         self._prefill_graphs = PrefillGraphs(self.state, self.weights, max_entries) if on else None
-
-    @property
-    def fused(self) -> bool:
-        return self._fused is not None
 
     @torch.no_grad()
     def decode_from_logits(self, logits, max_new_tokens: int, *, prompt_len: int,
@@ -251,8 +230,7 @@ class DecodeV2Loop:
         """Capture the greedy step once; on failure stay eager and keep the reason."""
         try:
             self.reset()
-            step = self._fused if self._fused is not None else greedy_decode
-            self._graph = capture_greedy(self.state, self.weights, warmup=2, step=step)
+            self._graph = capture_greedy(self.state, self.weights, warmup=2)
             self.graph_mode = "decodev2"
             self.graph_error = None
         except Exception as exc:  # noqa: BLE001 - reported, not swallowed

@@ -163,6 +163,7 @@ class PeerExchange:
         self.status = torch.zeros((), dtype=torch.int32, device=dev)
         peers = ChrNf4Peers()
         peers.rank, peers.world = comm.rank, comm.world
+        peers.capacity = self.max_rows
         for r, base in enumerate(ptrs):
             peers.recv[r] = base
             peers.flags[r] = base + 4 * n_recv
@@ -173,6 +174,9 @@ class PeerExchange:
         """The ``chr_nf4_peers_t`` to pass for this row-split matrix: carries the largest
         ``K_pad`` any rank holds for it, so that all ranks tile its rows alike. The first
         call per shape is a collective (max over ranks) and must happen outside capture."""
+        if int(mat.M) > self.max_rows:
+            raise ValueError(f"matrix has {mat.M} rows, the receive buffers were sized for "
+                             f"{self.max_rows}")
         key = (int(mat.M), int(mat.K_pad))
         got = self._per_shape.get(key)
         if got is None:

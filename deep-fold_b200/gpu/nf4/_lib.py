@@ -46,29 +46,6 @@ class ChrNf4Plan(Structure):
     ]
 
 
-class ChrNf4StepLayer(Structure):
-    """Mirror of ``chr_nf4_step_layer_t``."""
-
-    _fields_ = [(n, ChrNf4Dev) for n in ("q", "k", "v", "o", "gate", "up", "down")] + [
-        (n, c_void_p) for n in ("bq", "bk", "bv", "norm1", "norm2", "k_cache", "v_cache")
-    ]
-
-
-class ChrNf4Step(Structure):
-    """Mirror of ``chr_nf4_step_t``."""
-
-    _fields_ = (
-        [(n, c_int32) for n in ("n_layers", "hidden", "intermediate", "n_q", "n_kv", "head_dim",
-                                "max_seq", "vocab", "n_split", "fused_qkv", "commit")]
-        + [("rms_eps", c_float), ("attn_scale", c_float), ("eos", c_int64),
-           ("embed", ChrNf4Dev), ("embed_dense", c_void_p), ("lm_head", ChrNf4Dev)]
-        + [(n, c_void_p) for n in ("final_norm", "cos", "sin", "token", "position", "next_token",
-                                   "valid_len", "finished", "x", "q", "k", "v", "qkv", "attn",
-                                   "down_in", "logits", "attn_ws", "layers", "sync")]
-    )
-
-
-STEP_SYNC_BYTES = 8192
 AR_MAX_RANKS = 8
 AR_MAX_CTAS = 256
 
@@ -77,7 +54,7 @@ class ChrNf4Peers(Structure):
     """Mirror of ``chr_nf4_peers_t``."""
 
     _fields_ = [("rank", c_int32), ("world", c_int32), ("shape_k_pad", c_int32),
-                ("reserved", c_int32), ("recv", c_void_p * AR_MAX_RANKS),
+                ("capacity", c_int32), ("recv", c_void_p * AR_MAX_RANKS),
                 ("flags", c_void_p * AR_MAX_RANKS), ("epoch", c_void_p), ("status", c_void_p)]
 
 
@@ -96,6 +73,8 @@ SIGNATURES = {
     "chr_nf4_gemv": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
     "chr_nf4_gemv_f32": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
     "chr_nf4_gemv_shape": (c_int, [c_int32, c_int32, c_int32, POINTER(c_int32)]),
+    "chr_nf4_gemv_status": (c_int, []),
+    "chr_nf4_set_peer_polls": (None, [ctypes.c_uint32]),
     "chr_nf4_gemv_allreduce": (
         c_int, [_DEV, c_void_p, c_void_p, POINTER(ChrNf4Peers), c_void_p, c_void_p]
     ),
@@ -146,8 +125,6 @@ SIGNATURES = {
          c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p],
     ),
     "chr_nf4_silu_mul": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
-    "chr_nf4_decode_step": (c_int, [POINTER(ChrNf4Step), c_void_p]),
-    "chr_nf4_decode_step_status": (c_int, [c_void_p]),
     "chr_nf4_encode_f32": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int32]),
     "chr_nf4_decode_f32": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_int32]),
     "chr_nf4_encode_dev": (

@@ -139,8 +139,8 @@ int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y, void *stre
                      const void *add, const void *rms_w, float rms_eps);
 
 /* Work split the GEMV family uses for a matrix of n_rows x K_pad (swiglu != 0: the
- * gate/up pair): out = {R rows per warp, C 1024-wide chunks per warp, S K slices,
- * G row groups per CTA, tiles, CTAs}. Host-only (no launch); -3 when K_pad is beyond
+ * gate/up pair): out = {R rows per warp and tile, C 1024-wide chunks per warp, S K
+ * slices, G row groups per CTA, tiles, CTAs}. Host-only (no launch); -3 when K_pad is beyond
  * what the kernels cover. Ranks of a tensor-parallel group that pass the same
  * arguments get the same split, which chr_nf4_gemv_allreduce relies on. */
 int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu, int32_t out[6]);
@@ -155,12 +155,14 @@ int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu, int32_t ou
  * (same matrix shape, same GPU model), so a CTA only waits for its namesakes.
  * Buffers (all device memory, mapped into every rank's address space, e.g.
  * symmetric memory or CUDA IPC; zeroed once before the first call):
- *   recv[p]  rank p's receive buffer: 2 * world * M floats (two epochs x one slot
- *            per source rank), M up to the largest the buffers were sized for;
+ *   recv[p]  rank p's receive buffer: 2 * world * capacity floats (two epochs x
+ *            one slot of `capacity` rows per source rank); M > capacity -> -7;
  *   flags[p] rank p's flag words: world * CHR_NF4_AR_MAX_CTAS uint32;
  *   epoch    this rank's own uint32[2] {calls completed, exit ticket};
  *   status   this rank's own int32, set to 1 when a wait ran out of polls
- *            (2^22; the sum then includes whatever had arrived).
+ *            (2^22 unless chr_nf4_set_peer_polls changed it; the sum then
+ *            includes whatever had arrived, and later calls stop waiting until
+ *            the host clears the word).
  * All ranks must issue the same sequence of calls on these buffers and tile the
  * rows alike: when the ranks' K shares differ, each passes the largest K_pad of
  * the layer in shape_k_pad. Capturable
@@ -171,7 +173,7 @@ int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu, int32_t ou
 typedef struct {
   int32_t rank, world;
   int32_t shape_k_pad; /* 0, or the largest K_pad any rank holds for this layer (uneven shares) */
-  int32_t reserved;
+  int32_t capacity;    /* rows one source rank's slot of a receive buffer holds */
   void *recv[CHR_NF4_AR_MAX_RANKS];
   void *flags[CHR_NF4_AR_MAX_RANKS];
   void *epoch;
@@ -180,6 +182,16 @@ typedef struct {
 
 int chr_nf4_gemv_allreduce(const chr_nf4_dev_t *w, const void *x, void *y,
                            const chr_nf4_peers_t *peers, const void *add, void *stream);
+
+/* Poll budget of the peer-flag wait above (process-wide; 0 restores 2^22). A small
+ * budget lets a test see the wait run out without a peer having to fail. */
+void chr_nf4_set_peer_polls(uint32_t polls);
+
+/* Reads and clears the GEMV family's device status word (synchronises the device):
+ * 0 = fine; 3001 = a kernel found its shared-memory window smaller than its layout
+ * and did not run; 3002 = a bounded wait for a weight tile's bulk copy ran out and
+ * the kernel returned early. In both cases the launch's output is undefined. */
+int chr_nf4_gemv_status(void);
 
 /* Wide GEMM on activation rows: y_rows[N, M] = bf16( x_rows[N, K] . dequant(W)^T ),
  * the layout activations already have ([tokens, features], K contiguous), so no
@@ -287,71 +299,6 @@ int chr_nf4_rope_kv_rows(const void *q, int64_t q_stride, const void *k, int64_t
 /* out[n, i] = bf16( bf16(silu(g)) * u ) with g = gate_up[n, i], u = gate_up[n, I + i]:
  * the activation on the output of the stacked gate/up GEMM (bf16 [N, 2*I]). */
 int chr_nf4_silu_mul(const void *gate_up, void *out, int32_t N, int32_t I, void *stream);
-
-/* ---- Whole greedy step in one persistent launch ---------------------------
- * The sequence the reference issues as one launch per operation
- * (gpu/decodev2/step.py:162-187: embed row -> per layer [RMSNorm + q/k/v GEMV,
- * attention with fused RoPE and KV write, o-proj GEMV + residual, RMSNorm +
- * SwiGLU GEMV, down-proj GEMV + residual] -> final RMSNorm + lm_head GEMV ->
- * greedy pick -> commit) runs here as ONE cooperative kernel, one CTA per SM,
- * with a grid-wide barrier between operations; each CTA has the next
- * operation's first weight tile in flight while it waits at the barrier.
- * Results are bit-identical to the per-operation entry points above (same
- * device code, same work split). Every barrier wait is bounded: when it runs
- * out the kernel records a code in the sync block and runs to its end without
- * waiting again (the step's outputs are then undefined).
- * No counterpart in the reference's C ABI. */
-
-/* One decoder layer. A model with a fused, group-interleaved wqkv matrix
- * ([n_kv][n_rep + 2][head_dim] rows) passes it as q and leaves k.M = v.M = 0. */
-typedef struct {
-  chr_nf4_dev_t q, k, v, o, gate, up, down;
-  const void *bq, *bk, *bv; /* bf16 biases of q/k/v (of wqkv in bq), or NULL */
-  const void *norm1, *norm2; /* bf16 [hidden] RMSNorm weights */
-  void *k_cache, *v_cache;   /* bf16 [max_seq, n_kv, head_dim] */
-} chr_nf4_step_layer_t;
-
-#define CHR_NF4_STEP_SYNC_BYTES 8192
-
-typedef struct {
-  int32_t n_layers, hidden, intermediate, n_q, n_kv, head_dim, max_seq, vocab;
-  int32_t n_split;     /* attention splits the workspace was sized for (1..64) */
-  int32_t fused_qkv;   /* 1: layers carry wqkv in q, activations go through qkv */
-  int32_t commit;      /* 1: token/position/finished advance; 0: next_token and position only */
-  float rms_eps, attn_scale;
-  int64_t eos;
-  chr_nf4_dev_t embed;       /* packed embedding table, or packed == NULL ... */
-  const void *embed_dense;   /* ... and a bf16 [vocab, hidden] table here */
-  chr_nf4_dev_t lm_head;
-  const void *final_norm;
-  const void *cos, *sin;     /* bf16 [max_seq, head_dim] */
-  void *token, *position, *next_token; /* device int64 */
-  void *valid_len;           /* device int32 */
-  void *finished;            /* device uint8 */
-  void *x, *q, *k, *v, *qkv, *attn, *down_in, *logits; /* bf16 activations */
-  float *attn_ws;            /* n_q * n_split * (head_dim + 2) floats */
-  const chr_nf4_step_layer_t *layers; /* HOST array of n_layers (<= 96) descriptors, read at the call */
-  void *sync;                /* CHR_NF4_STEP_SYNC_BYTES device bytes, zeroed once by the caller */
-} chr_nf4_step_t;
-
-/* Launches one step on `stream`. Returns CHR_* codes; -3 when a shape is outside
- * what the persistent kernel covers (K beyond 24576, head_dim > 256, hidden not a
- * multiple of 8, more than 96 layers, a layer whose matrices do not have the
- * model's dimensions) - use the per-operation entry points then. Capturable; not
- * re-entrant (call it from one thread at a time). */
-int chr_nf4_decode_step(const chr_nf4_step_t *step, void *stream);
-
-/* Profiling aid: the sync block also records, for the last launch, nanosecond
- * stamps taken by CTA 0 (64-bit words starting at byte CHR_NF4_STEP_STAMPS_OFFSET:
- * [0] kernel start, [n] the moment the barrier wait before operation n
- * completed; operation 1 is layer 0's q/k/v, then attention, o, gate/up, down
- * per layer, then lm_head and the pick). */
-#define CHR_NF4_STEP_STAMPS_OFFSET 4160
-
-/* Reads (and clears) the status word of a sync block; synchronises the device.
- * 0 = every barrier completed; 1..999 = the wait before operation n gave up;
- * 1000 = a token id outside the embedding table was fed (its row reads as zero). */
-int chr_nf4_decode_step_status(void *sync);
 
 #ifdef __cplusplus
 }

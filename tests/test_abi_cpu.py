@@ -46,29 +46,23 @@ def test_struct_layout_is_the_frozen_one():
     assert ctypes.sizeof(ChrNf4Plan) == 48 and ChrNf4Plan.ws_floats.offset == 40
 
 
-def test_step_structs_match_the_header(tmp_path):
-    """sizeof / offsetof of the persistent-step structs as the C compiler sees them."""
+def test_peer_struct_matches_the_header(tmp_path):
+    """sizeof / offsetof of the peer-exchange struct as the C compiler sees it."""
     import subprocess
 
-    from gpu.nf4._lib import (AR_MAX_CTAS, AR_MAX_RANKS, STEP_SYNC_BYTES, ChrNf4Peers, ChrNf4Step,
-                              ChrNf4StepLayer)
+    from gpu.nf4._lib import AR_MAX_CTAS, AR_MAX_RANKS, ChrNf4Peers
 
     src = tmp_path / "sz.c"
     src.write_text(
         '#include <stdio.h>\n#include <stddef.h>\n#include "chr_gpu.h"\n'
-        'int main(void) { printf("%zu %zu %zu %zu %zu %zu %d %d %zu %zu %zu %d %d\\n", sizeof(chr_nf4_step_t), '
-        "sizeof(chr_nf4_step_layer_t), offsetof(chr_nf4_step_t, eos), offsetof(chr_nf4_step_t, lm_head), "
-        "offsetof(chr_nf4_step_t, sync), offsetof(chr_nf4_step_layer_t, norm1), "
-        "CHR_NF4_STEP_SYNC_BYTES, CHR_NF4_STEP_STAMPS_OFFSET, sizeof(chr_nf4_peers_t), "
-        "offsetof(chr_nf4_peers_t, recv), offsetof(chr_nf4_peers_t, epoch), CHR_NF4_AR_MAX_RANKS, "
-        "CHR_NF4_AR_MAX_CTAS); return 0; }\n")
+        'int main(void) { printf("%zu %zu %zu %zu %d %d\\n", sizeof(chr_nf4_peers_t), '
+        "offsetof(chr_nf4_peers_t, capacity), offsetof(chr_nf4_peers_t, recv), "
+        "offsetof(chr_nf4_peers_t, epoch), CHR_NF4_AR_MAX_RANKS, CHR_NF4_AR_MAX_CTAS); return 0; }\n")
     exe = tmp_path / "sz"
     subprocess.run(["gcc", f"-I{ROOT / 'include'}", str(src), "-o", str(exe)], check=True)
     got = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True,
                                           text=True).stdout.split()]
-    assert got == [ctypes.sizeof(ChrNf4Step), ctypes.sizeof(ChrNf4StepLayer), ChrNf4Step.eos.offset,
-                   ChrNf4Step.lm_head.offset, ChrNf4Step.sync.offset, ChrNf4StepLayer.norm1.offset,
-                   STEP_SYNC_BYTES, 4160, ctypes.sizeof(ChrNf4Peers), ChrNf4Peers.recv.offset,
+    assert got == [ctypes.sizeof(ChrNf4Peers), ChrNf4Peers.capacity.offset, ChrNf4Peers.recv.offset,
                    ChrNf4Peers.epoch.offset, AR_MAX_RANKS, AR_MAX_CTAS]
 
 

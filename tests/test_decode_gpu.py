@@ -246,49 +246,6 @@ def test_host_seats_linear_and_embedding(golden):
     assert torch.equal(dequant_nf4_rows(emb.packed, emb.scale, ids, 200), rows.view(5, 200))
 
 
-@pytest.mark.parametrize("spec,seed,kw", [
-    (TINY_LLAMA, 0, {}),
-    (TINY_INTERNLM, 1, {}),
-    (MEDIUM_LLAMA, 0, {}),
-    (MEDIUM_LLAMA, 0, {"packed_embed": True}),
-])
-def test_persistent_step_is_bit_identical_to_the_launch_chain(spec, seed, kw):
-    _, state, weights = session(spec, seed, **kw)
-    prompt = [1, 3, 5, 7]
-    loop = DecodeV2Loop(state, weights)
-    chain = loop.generate_device_window(prompt, 10)
-    want_logits = state.arena.logits.clone()
-    want_k, want_v = state.kv.k.clone(), state.kv.v.clone()
-    assert loop.enable_fused_step() is None and loop.fused
-    fused = loop.generate_device_window(prompt, 10)
-    assert loop._fused.status() == 0
-    assert fused.tokens == chain.tokens
-    assert torch.equal(state.arena.logits, want_logits)
-    assert torch.equal(state.kv.k, want_k) and torch.equal(state.kv.v, want_v)
-    assert loop.capture_graphs() == "decodev2", loop.graph_error
-    replay = loop.generate_device_window(prompt, 10)
-    assert loop._fused.status() == 0
-    assert replay.tokens == chain.tokens and torch.equal(state.arena.logits, want_logits)
-    # host-visible requests through the same step
-    assert loop.generate(prompt, 6).tokens == chain.tokens[:6]
-    loop.enable_fused_step(False)
-    assert not loop.fused and loop.generate_device_window(prompt, 10).tokens == chain.tokens
-
-
-def test_persistent_step_flags_a_bad_token_id_and_refuses_shards():
-    from gpu.decodev2 import FusedStep, fused_step_supported
-
-    _, state, weights = session(TINY_LLAMA, 0)
-    step = FusedStep(state, weights)
-    state.reset()
-    state.token.fill_(state.spec.vocab + 5)
-    step(state, weights)
-    assert step.status() == 1000 and step.status() == 0
-    with pytest.raises(RuntimeError):
-        step(state, DeviceWeights.from_synth(build(TINY_LLAMA, 0), "cuda", torch.bfloat16))
-    assert fused_step_supported(state, weights) is None
-
-
 def test_prefill_graphs_replay_equals_eager():
     _, state, weights = session(MEDIUM_LLAMA, 0)
     loop = DecodeV2Loop(state, weights)

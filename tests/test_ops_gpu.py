@@ -57,7 +57,7 @@ def assert_close(got: torch.Tensor, want: np.ndarray, what=""):
 GEMV_SHAPES = [
     (2048, 2048), (256, 2048), (11008, 2048), (2048, 11008), (5120, 5120), (1024, 5120),
     (5120, 13824), (6144, 16384), (5120, 27648), (130, 65), (7, 64), (1, 4096), (333, 1000),
-    (4096, 4096), (64, 32768),
+    (4096, 4096), (64, 30080), (2051, 2752),
 ]
 
 
@@ -75,6 +75,42 @@ def test_gemv_matches_oracle(m, k):
     # repeat is bit-identical
     y2 = nf4_gemv(pt, st, xt, m, k, o.padded_k(k))
     assert torch.equal(y, y2)
+
+
+def test_gemv_rejects_k_beyond_what_a_cta_stages_and_reports_no_status():
+    """x is staged in shared memory beside the lookup table: K up to 30080."""
+    from gpu.nf4 import _lib, nf4_gemv
+
+    k = 30144
+    p, s, pt, st = blobs(8, k, 5)
+    xt = torch.zeros(k, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match=r"\(-3\)"):
+        nf4_gemv(pt, st, xt, 8, k, o.padded_k(k))
+    assert _lib.load().chr_nf4_gemv_status() == 0
+
+
+def test_gemv_with_scales_off_the_16_byte_grid():
+    """A scale blob that starts 2 bytes past a 16-byte boundary cannot ride the bulk
+    copies: the kernel fetches scales from global memory instead, same results."""
+    from gpu.nf4 import _lib
+    from gpu.nf4._lib import ChrNf4Dev
+
+    m, k = 515, 4096
+    rng = np.random.default_rng(77)
+    p, s, pt, st = blobs(m, k, 3, weight_like=True)
+    xt, xf = bf16_vec(rng, k)
+    shifted = torch.empty(st.numel() + 8, dtype=st.dtype, device="cuda")
+    off = shifted[1:1 + st.numel()].view(st.shape)
+    off.copy_(st)
+    assert off.data_ptr() % 16 == 2
+    y = torch.empty(m, dtype=torch.bfloat16, device="cuda")
+    w = ChrNf4Dev(m, k, o.padded_k(k), pt.data_ptr(), off.data_ptr())
+    rc = _lib.load().chr_nf4_gemv(w, xt.data_ptr(), y.data_ptr(),
+                                  torch.cuda.current_stream().cuda_stream, None, None, 1e-6)
+    assert rc == 0
+    want = o.dequantize(p, s, m, k).astype(np.float64) @ xf.astype(np.float64)
+    assert_close(y.reshape(m, 1), want.astype(np.float32).reshape(m, 1), "gemv, unaligned scales")
+    assert _lib.load().chr_nf4_gemv_status() == 0
 
 
 def test_gemv_pad_garbage_is_ignored():
