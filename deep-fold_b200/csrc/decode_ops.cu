@@ -89,6 +89,38 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const AttnArgs
                   [] { __syncthreads(); });
 }
 
+// The same items for B sequences in one launch: grid.y = B * n_kv; every sequence has
+// its own q, current k/v, cache, output, split partials, valid length and position
+// (consecutive blocks of the per-sequence sizes).
+struct AttnBatch {
+  int batch;
+  long long q_stride, kv_act_stride, cache_stride, out_stride, ws_stride;
+};
+
+template <int P, int H>
+__global__ void __launch_bounds__(kAttnThreads) attn_batch_kernel(const AttnArgs proto,
+                                                                 const AttnBatch bt) {
+  __shared__ AttnSmem<P, H> sm;
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.y / proto.n_kv;
+  const int kvh = blockIdx.y - b * proto.n_kv;
+  AttnArgs a = proto;
+  a.q += b * bt.q_stride;
+  if (a.k_act != nullptr) a.k_act += b * bt.kv_act_stride;
+  if (a.v_act != nullptr) a.v_act += b * bt.kv_act_stride;
+  a.k_cache += b * bt.cache_stride;
+  a.v_cache += b * bt.cache_stride;
+  a.out += b * bt.out_stride;
+  a.m_s += b * bt.ws_stride;
+  a.l_s += b * bt.ws_stride;
+  a.o_s += b * bt.ws_stride;
+  a.valid_len += b;
+  if (a.position != nullptr) a.position += b;
+  unsigned int *ctr = &g_attn_arrivals[(blockIdx.y * gridDim.z + blockIdx.z) % kMaxAttnGroups];
+  attn_item<P, H>(a, sm, blockIdx.x, kvh, blockIdx.z, ctr, threadIdx.x, [] { __syncthreads(); });
+}
+
 // ----------------------------------------------------------------------------
 // Packed embedding rows  (reference: gpu/host/embedding.py:74-107)
 // ----------------------------------------------------------------------------
@@ -278,6 +310,69 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
   return e == cudaSuccess ? kOk : kLaunch;
 }
 
+extern "C" int chr_nf4_attn_batch(const void *q, const void *k, const void *v, void *out,
+                                  const void *valid_len, float *ws, int32_t batch, int32_t n_q,
+                                  int32_t n_kv, int32_t hd, int32_t n_split, float scale,
+                                  void *stream, const void *k_act, const void *v_act,
+                                  const void *cos, const void *sin, const void *position,
+                                  int32_t max_seq) {
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || valid_len == nullptr ||
+      ws == nullptr) {
+    return kNull;
+  }
+  if (batch < 1 || n_q < 1 || n_kv < 1 || hd < 2 || hd > 256 || (hd & 1) != 0 ||
+      (n_q % n_kv) != 0 || n_split < 1 || n_split > 64 || max_seq < 1) {
+    return kDims;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_split > kAttnMaxSplit) n_split = kAttnMaxSplit;
+  const int slots = n_q * n_split;
+  const int n_rep = n_q / n_kv;
+  AttnArgs a{};
+  a.q = static_cast<const __nv_bfloat16 *>(q);
+  a.q_group_stride = n_rep * hd;
+  a.k_act = static_cast<const __nv_bfloat16 *>(k_act);
+  a.v_act = static_cast<const __nv_bfloat16 *>(v_act);
+  a.kv_act_stride = hd;
+  a.k_cache = static_cast<const __nv_bfloat16 *>(k);
+  a.v_cache = static_cast<const __nv_bfloat16 *>(v);
+  a.out = static_cast<__nv_bfloat16 *>(out);
+  a.m_s = ws;
+  a.l_s = ws + slots;
+  a.o_s = ws + 2 * slots;
+  a.valid_len = static_cast<const int32_t *>(valid_len);
+  a.cos = static_cast<const __nv_bfloat16 *>(cos);
+  a.sin = static_cast<const __nv_bfloat16 *>(sin);
+  a.position = static_cast<const int64_t *>(position);
+  a.n_q = n_q;
+  a.n_kv = n_kv;
+  a.hd = hd;
+  a.n_split = n_split;
+  a.max_seq = max_seq;
+  a.scale = scale;
+  AttnBatch bt{};
+  bt.batch = batch;
+  bt.q_stride = static_cast<long long>(n_q) * hd;
+  bt.kv_act_stride = static_cast<long long>(n_kv) * hd;
+  bt.cache_stride = static_cast<long long>(max_seq) * n_kv * hd;
+  bt.out_stride = static_cast<long long>(n_q) * hd;
+  bt.ws_stride = static_cast<long long>(slots) * (hd + 2);
+  const int heads_per_item = hd <= 128 ? 8 : 4;
+  const int chunks = (n_rep + heads_per_item - 1) / heads_per_item;
+  if (static_cast<long long>(batch) * n_kv * chunks > kMaxAttnGroups) return kDims;
+  const dim3 grid(static_cast<unsigned>(n_split), static_cast<unsigned>(batch * n_kv),
+                  static_cast<unsigned>(chunks));
+  cudaError_t e;
+  if (hd <= 64) {
+    e = launch_chain(attn_batch_kernel<1, 8>, grid, dim3(kAttnThreads), 0, st, a, bt);
+  } else if (hd <= 128) {
+    e = launch_chain(attn_batch_kernel<2, 8>, grid, dim3(kAttnThreads), 0, st, a, bt);
+  } else {
+    e = launch_chain(attn_batch_kernel<4, 4>, grid, dim3(kAttnThreads), 0, st, a, bt);
+  }
+  return e == cudaSuccess ? kOk : kLaunch;
+}
+
 extern "C" int chr_nf4_embed_rows(const chr_nf4_dev_t *w, const void *ids, int32_t n, void *out,
                                   void *status, const void *position, void *valid_len,
                                   void *stream) {
@@ -334,7 +429,11 @@ constexpr int kMaxDevices = 64;
 float *g_static_ws_ptr[kMaxDevices] = {};
 
 // The array's name is only a stand-in on the host; the kernel needs the address
-// the current device gives it. Looked up once per device, with that device current.
+// the current device gives it. Looked up once per device, with that device current
+// (the caller's `stream` must belong to the current device: the address handed to
+// the kernel is the current device's copy of the array). The cache below is written
+// without a lock: two host threads that race on a device's first call both store
+// the same address.
 int static_ws_for_current_device(float **out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return chr::kLaunch;
@@ -356,7 +455,7 @@ extern "C" int chr_nf4_attn_noalloc(const void *q, const void *k, const void *v,
                                     const void *v_act, const void *cos, const void *sin,
                                     const void *position, int32_t max_seq) {
   if (n_q < 1 || hd < 2 || n_split < 1 || n_split > 64) return chr::kDims;
-  const long long used_splits = n_split > 16 ? 16 : n_split;
+  const long long used_splits = n_split > chr::kAttnMaxSplit ? chr::kAttnMaxSplit : n_split;
   if (static_cast<long long>(n_q) * used_splits * (hd + 2) > kStaticAttnFloats) {
     return chr::kWorkspace;  // beyond the built-in scratch: use chr_nf4_attn with a caller buffer
   }

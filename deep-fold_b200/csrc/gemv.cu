@@ -234,6 +234,8 @@ GemvArgs one_matrix(const chr_nf4_dev_t *w, const void *x, const void *add, cons
 }  // namespace
 }  // namespace chr
 
+#include "gemv_n.cuh"  // N-column GEMV: same translation unit, it shares the status word
+
 using namespace chr;
 
 extern "C" int chr_nf4_gemv(const chr_nf4_dev_t *w, const void *x, void *y, void *stream,

@@ -7,6 +7,7 @@ from collections.abc import Sequence
 
 import torch
 
+from .graph import capture_on_side_stream
 from .linear import DeviceWeights
 from .prefill import forward_prefill, prefill_chunk_width
 from .state import DecodeState
@@ -46,14 +47,8 @@ class PrefillGraphs:
             return
         forward_prefill(self.state, self.weights, ids, start=start, logits=logits)
         static_ids = ids.clone()
-        graph = torch.cuda.CUDAGraph()
-        main = torch.cuda.current_stream()
-        side = torch.cuda.Stream()
-        side.wait_stream(main)
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                forward_prefill(self.state, self.weights, static_ids, start=start, logits=logits)
-        main.wait_stream(side)
+        graph = capture_on_side_stream(
+            lambda: forward_prefill(self.state, self.weights, static_ids, start=start, logits=logits))
         while len(self._cache) >= self.max_entries:
             self._cache.pop(next(iter(self._cache)))
         self._cache[key] = (static_ids, graph)

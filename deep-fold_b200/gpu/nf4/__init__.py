@@ -33,6 +33,9 @@ __all__ = [
     "nf4_gemv",
     "nf4_gemv_allreduce",
     "nf4_gemv_f32",
+    "nf4_gemv_n",
+    "nf4_attn_batch",
+    "GEMV_MAX_N",
     "nf4_pick_commit",
     "nf4_plan",
     "nf4_qkv",
@@ -47,6 +50,7 @@ __all__ = [
     "nf4_version",
 ]
 
+GEMV_MAX_N = 8
 ATTN_SPLIT = 32
 
 
@@ -284,6 +288,53 @@ def nf4_gemv(
     return y
 
 
+_GEMV_N_WS: dict = {}
+
+
+def nf4_gemv_n(
+    packed: torch.Tensor,
+    scale: torch.Tensor,
+    x_rows: torch.Tensor,
+    M: int,  # noqa: N803
+    K: int,  # noqa: N803
+    K_pad: int,  # noqa: N803
+    out: torch.Tensor | None = None,
+    add: torch.Tensor | None = None,
+    bias: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """``y[N, M] = x_rows[N, K] @ dequant(W).T (+ bias) (+ add)`` for ``N`` in 1..8 on the
+    CUDA cores, with the GEMV's numerics (FP32 weights). ``out`` and ``add`` may alias.
+    The FP32 split-K workspace large K needs is kept per (device, size) and reused."""
+    if not x_rows.is_cuda or x_rows.dtype is not torch.bfloat16:
+        _fail("x_rows must be CUDA bfloat16")
+    if x_rows.dim() != 2 or x_rows.size(1) != int(K):
+        _fail("x_rows must be [N, K]")
+    n = int(x_rows.size(0))
+    if not 1 <= n <= GEMV_MAX_N:
+        _fail(f"nf4_gemv_n takes 1..{GEMV_MAX_N} rows, got {n}")
+    dev, keep = _matrix(packed, scale, M, K, K_pad)
+    x_rows = x_rows.contiguous()
+    if out is None:
+        out = torch.empty((n, int(M)), dtype=torch.bfloat16, device=x_rows.device)
+    else:
+        _out_vec(out, n * int(M))
+    add_t = _opt_bf16(add, n * int(M), "add", exact=False)
+    bias_t = _opt_bf16(bias, int(M), "bias", exact=True)
+    lib = _lib.load()
+    need = int(lib.chr_nf4_gemv_n_ws(ctypes.byref(dev), n))
+    ws = None
+    if need:
+        key = (x_rows.device, need)
+        ws = _GEMV_N_WS.get(key)
+        if ws is None:
+            ws = _GEMV_N_WS[key] = torch.empty(need, dtype=torch.float32, device=x_rows.device)
+    rc = lib.chr_nf4_gemv_n(ctypes.byref(dev), _ptr(x_rows), _ptr(out), n, _ptr(add_t), _ptr(bias_t),
+                            _ptr(ws), need, _stream())
+    _lib.check(rc, "chr_nf4_gemv_n")
+    del keep
+    return out
+
+
 def nf4_gemv_f32(
     packed: torch.Tensor,
     scale: torch.Tensor,
@@ -473,6 +524,54 @@ def nf4_rope_kv(
         _ptr(sin.contiguous()), _ptr(pos), n_q, n_kv, hd, max_seq, _stream(),
     )
     _lib.check(rc, "chr_nf4_rope_kv")
+
+
+def nf4_attn_batch(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    valid_len: torch.Tensor,
+    scale: float,
+    ws: torch.Tensor,
+    n_split: int,
+    k_act: torch.Tensor,
+    v_act: torch.Tensor,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    position: torch.Tensor,
+) -> None:
+    """``nf4_attn`` for ``B`` independent sequences in one launch: ``q [B, n_q, hd]``,
+    ``k``/``v`` caches ``[B, max_seq, n_kv, hd]``, ``k_act``/``v_act [B, n_kv, hd]``,
+    ``out [B, n_q*hd]``, ``valid_len`` int32 ``[B]``, ``position`` int64 ``[B]``."""
+    for t, what in ((q, "q"), (k, "k"), (v, "v"), (out, "out"), (k_act, "k_act"), (v_act, "v_act"),
+                    (cos, "cos"), (sin, "sin")):
+        if not t.is_cuda or t.dtype is not torch.bfloat16 or not t.is_contiguous():
+            _fail(f"{what} must be a contiguous CUDA bf16 tensor")
+    if k.dim() != 4 or k.shape != v.shape:
+        _fail("caches must be [B, max_seq, n_kv, hd]")
+    b, max_seq, n_kv, hd = (int(d) for d in k.shape)
+    if q.dim() != 3 or int(q.size(0)) != b or int(q.size(2)) != hd:
+        _fail("q must be [B, n_q, hd]")
+    n_q = int(q.size(1))
+    if out.numel() < b * n_q * hd or k_act.numel() != b * n_kv * hd or v_act.numel() != b * n_kv * hd:
+        _fail("out / k_act / v_act sizes")
+    if tuple(cos.shape) != (max_seq, hd) or tuple(sin.shape) != (max_seq, hd):
+        _fail("cos / sin shape")
+    if valid_len.dtype is not torch.int32 or valid_len.numel() != b or not valid_len.is_cuda:
+        _fail("valid_len must be CUDA int32 [B]")
+    if position.dtype is not torch.int64 or position.numel() != b or not position.is_cuda:
+        _fail("position must be CUDA int64 [B]")
+    n_split = int(n_split)
+    if not 1 <= n_split <= 64:
+        _fail("n_split must be 1..64")
+    if ws.dtype is not torch.float32 or not ws.is_cuda or ws.numel() < b * n_q * min(n_split, 16) * (hd + 2):
+        _fail("attn workspace too small")
+    rc = _lib.load().chr_nf4_attn_batch(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(valid_len), _ptr(ws), b, n_q, n_kv, hd, n_split,
+        float(scale), _stream(), _ptr(k_act), _ptr(v_act), _ptr(cos), _ptr(sin), _ptr(position),
+        max_seq)
+    _lib.check(rc, "chr_nf4_attn_batch")
 
 
 def nf4_attn(

@@ -74,6 +74,10 @@ SIGNATURES = {
     "chr_nf4_gemv_f32": (c_int, [_DEV, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
     "chr_nf4_gemv_shape": (c_int, [c_int32, c_int32, c_int32, POINTER(c_int32)]),
     "chr_nf4_gemv_status": (c_int, []),
+    "chr_nf4_gemv_n_ws": (c_int64, [_DEV, c_int32]),
+    "chr_nf4_gemv_n": (
+        c_int, [_DEV, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
+    ),
     "chr_nf4_set_peer_polls": (None, [ctypes.c_uint32]),
     "chr_nf4_gemv_allreduce": (
         c_int, [_DEV, c_void_p, c_void_p, POINTER(ChrNf4Peers), c_void_p, c_void_p]
@@ -96,6 +100,12 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
          c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_int32],
+    ),
+    "chr_nf4_attn_batch": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+         c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int32],
     ),
     "chr_nf4_attn_noalloc": (
         c_int,

@@ -112,13 +112,31 @@ int chr_nf4_rope_kv(void *q, void *k, const void *v, void *k_cache, void *v_cach
  * position (device int64) q is rotated in FP32; with k_act/v_act as well, the
  * rotated current k and the current v are written to cache row *position and
  * the current token is attended with those unrounded FP32 values.
- * hd <= 256, hd % 8 == 0, n_split in [1, 64].
+ * hd <= 256, hd % 8 == 0, n_split in [1, 64] (at most 16 splits are used).
+ * Cross-call state: the splits of a kv head are merged by the last CTA to arrive,
+ * counted in a small array inside the library that every call leaves zeroed. Calls
+ * that follow each other on one stream (or are otherwise ordered) are fine; two
+ * attention launches that overlap on the device (different streams) share those
+ * counters and must be serialised by the caller.
  * Replaces gpu/include/chr_gpu.h:123 ; kernels gpu/nf4/nf4_gemv.cu:599-727. */
 int chr_nf4_attn(const void *q, const void *k, const void *v, void *out,
                  const void *valid_len, float *ws, int32_t n_q, int32_t n_kv,
                  int32_t hd, int32_t n_split, float scale, void *stream,
                  const void *k_act, const void *v_act, const void *cos,
                  const void *sin, const void *position, int32_t max_seq);
+
+/* chr_nf4_attn for `batch` independent sequences in one launch (batched decode):
+ * q [batch, n_q, hd], k_act / v_act [batch, n_kv, hd], k / v caches
+ * [batch, max_seq, n_kv, hd], out [batch, n_q*hd], valid_len int32 [batch],
+ * position int64 [batch], ws batch * n_q*min(n_split,16)*(hd+2) floats; cos / sin
+ * are shared. batch * n_kv * ceil(n_rep / 8) must not exceed 1024 (-3). Same
+ * arithmetic per sequence as chr_nf4_attn. No counterpart in the reference, whose
+ * decode is one sequence (gpu/nf4/nf4_gemv.cu:599-727). */
+int chr_nf4_attn_batch(const void *q, const void *k, const void *v, void *out,
+                       const void *valid_len, float *ws, int32_t batch, int32_t n_q,
+                       int32_t n_kv, int32_t hd, int32_t n_split, float scale, void *stream,
+                       const void *k_act, const void *v_act, const void *cos,
+                       const void *sin, const void *position, int32_t max_seq);
 
 /* y[i] = bf16( w[i] * x[i] * rsqrt(mean(x^2) + eps) ); x, w, y bf16 [n].
  * Replaces gpu/include/chr_gpu.h:133 ; kernel gpu/nf4/nf4_gemv.cu:729-751. */
@@ -137,6 +155,21 @@ const char *chr_nf4_version(void);
  * ranks before the single bf16 rounding. add: optional bf16 [M] (e.g. a bias). */
 int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y, void *stream,
                      const void *add, const void *rms_w, float rms_eps);
+
+/* GEMV for N = 1..8 activation rows on CUDA cores: y_rows[n, :] = bf16( dequant(W) .
+ * x_rows[n, :] (+ bias) (+ add_rows[n, :]) ) with the numerics of chr_nf4_gemv (FP32
+ * weights LUT*scale, never rounded to bf16; FP32 accumulation; one rounding). Every
+ * packed weight is read from HBM once and dequantized once for all N rows, which is
+ * what batched decode wants where the tensor-core GEMM's bf16 weights are not.
+ * x_rows bf16 [N, K]; y_rows bf16 [N, M]; add_rows optional bf16 [N, M] (may alias
+ * y_rows); bias optional bf16 [M]. Large K is cut into slices whose FP32 partials go
+ * to ws ([slices, N, M]); chr_nf4_gemv_n_ws says how many floats that takes (0 when
+ * one slice covers K); a missing or small ws -> -7; N outside 1..8 -> -2.
+ * No counterpart in the reference (its GEMV is N = 1, gpu/nf4/nf4_gemv.cu:291-324). */
+int64_t chr_nf4_gemv_n_ws(const chr_nf4_dev_t *w, int32_t N);
+int chr_nf4_gemv_n(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows, int32_t N,
+                   const void *add_rows, const void *bias, float *ws, int64_t ws_floats,
+                   void *stream);
 
 /* Work split the GEMV family uses for a matrix of n_rows x K_pad (swiglu != 0: the
  * gate/up pair): out = {R rows per warp and tile, C 1024-wide chunks per warp, S K
@@ -248,7 +281,7 @@ int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_token,
  * n_q * min(n_split, 16) * (hd + 2) exceeds 262144 floats. It calls no
  * allocation routine. The first call on a device looks the array's address up
  * (one host-side runtime query) and should therefore come before any stream
- * capture on that device. All calls share the array: nothing in it has to start
+ * capture on that device; the device that owns `stream` must be the current one. All calls share the array: nothing in it has to start
  * at zero, but two calls that overlap on the GPU (different streams, or another
  * process thread) race on it and must be serialised by the caller. */
 int chr_nf4_attn_noalloc(const void *q, const void *k, const void *v, void *out,

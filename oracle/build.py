@@ -35,8 +35,19 @@ def build_c() -> Path:
     return C_LIB
 
 
-def build_reference_kernels(reference_root: str | os.PathLike = "/root/reference") -> Path | None:
-    root = Path(reference_root)
+def reference_checkout() -> Path | None:
+    """Where the reference's sources are: ``--reference DIR`` on the command line or the
+    ``DEEPFOLD_REFERENCE`` environment variable. There is no built-in default."""
+    if "--reference" in sys.argv[1:-1]:
+        return Path(sys.argv[sys.argv.index("--reference") + 1])
+    env = os.environ.get("DEEPFOLD_REFERENCE")
+    return Path(env) if env else None
+
+
+def build_reference_kernels(reference_root: str | os.PathLike | None = None) -> Path | None:
+    root = Path(reference_root) if reference_root is not None else reference_checkout()
+    if root is None:
+        return REF_LIB if REF_LIB.exists() else None
     srcs = [root / "gpu" / "nf4" / "nf4_gemv.cu", root / "gpu" / "nf4" / "nf4_gemm.cu"]
     if not all(s.is_file() for s in srcs):
         return REF_LIB if REF_LIB.exists() else None
@@ -51,9 +62,9 @@ def build_reference_kernels(reference_root: str | os.PathLike = "/root/reference
     return REF_LIB
 
 
-def build() -> list[str]:
+def build(reference_root: str | os.PathLike | None = None) -> list[str]:
     out = [f"built {build_c()}"]
-    ref = build_reference_kernels()
+    ref = build_reference_kernels(reference_root)
     out.append(f"reference kernels: {ref}" if ref else "reference kernels: checkout absent, not built")
     return out
 

@@ -132,7 +132,9 @@ def rope() -> None:
 
 
 def main() -> None:
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference").resolve()
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <reference checkout>")
+    root = Path(sys.argv[1]).resolve()
     sys.path.insert(0, str(root))
     import gpu.tests.nf4_oracle as ref
 

@@ -147,3 +147,51 @@ def test_ops_reject_cpu_tensors_before_any_launch():
         nf4_rms(x, x, x, 1e-6)
     with pytest.raises(RuntimeError, match="max_n"):
         nf4_gemm(packed, scale, x, 4, 64, 64, max_n=65)
+
+
+def test_no_entry_point_allocates_device_memory():
+    """Source scan of the library for allocation calls (the reference gates its own
+    kernels the same way, gpu/tests/oracle_gate.py:558-582): every buffer is the caller's."""
+    import re
+
+    banned = re.compile(r"\b(cudaMalloc\w*|cudaHostAlloc|cudaFree\w*|cuMemAlloc\w*|malloc|calloc|realloc)\s*\(")
+    hits = []
+    for src in sorted((ROOT / "deep-fold_b200" / "csrc").glob("*")):
+        if src.suffix not in (".cu", ".cuh", ".cpp", ".h"):
+            continue
+        if src.name == "codec.cpp":
+            continue  # the host-side codec works on host memory only (std::vector / threads)
+        for no, line in enumerate(src.read_text().splitlines(), 1):
+            code = line.split("//")[0]
+            if banned.search(code):
+                hits.append(f"{src.name}:{no}: {line.strip()}")
+    assert not hits, "\n".join(hits)
+
+
+def test_the_reference_binding_compiles_against_this_header(tmp_path):
+    """gpu/nf4/bindings.cpp of the reference (its torch/pybind layer over the C ABI) must
+    build unchanged against include/chr_gpu.h: same structs, entry names and signatures."""
+    import os
+    import subprocess
+    import sysconfig
+
+    sibling = ROOT.parent / "reference"
+    where = os.environ.get("DEEPFOLD_REFERENCE") or (str(sibling) if sibling.is_dir() else None)
+    src = None if where is None else Path(where) / "gpu" / "nf4" / "bindings.cpp"
+    if src is None or not src.is_file():
+        pytest.skip("no reference checkout here (DEEPFOLD_REFERENCE): nothing to compile")
+    from torch.utils.cpp_extension import include_paths
+
+    # the binding includes "chr_gpu.h" from its own include directory: point that name at ours
+    inc = tmp_path / "inc"
+    inc.mkdir()
+    (inc / "chr_gpu.h").write_text((ROOT / "include" / "chr_gpu.h").read_text())
+    cmd = ["g++", "-std=c++17", "-fsyntax-only", "-w", f"-I{inc}",
+           f"-I{sysconfig.get_paths()['include']}", "-DTORCH_EXTENSION_NAME=chr_nf4_ext",
+           "-DTORCH_API_INCLUDE_EXTENSION_H"]
+    cmd += [f"-I{p}" for p in include_paths()]
+    cuda_inc = Path("/usr/local/cuda/include")
+    if cuda_inc.is_dir():
+        cmd.append(f"-I{cuda_inc}")
+    res = subprocess.run(cmd + [str(src)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]

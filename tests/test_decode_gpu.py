@@ -208,6 +208,24 @@ def test_token_loop_mma_path_tracks_decode_v2():
     loop.prefill_from(prompt, 0)
     loop.state.token.copy_(loop.state.next_token)
     assert loop.step() == eager[1]
+    # teacher-forced through the MMA step: its logits stay within the tolerance of the
+    # float32 oracle at every position, and the argmax agrees wherever the oracle's
+    # top-2 margin is more than a few bf16 ulps (the reference's own protocol for its
+    # MMA loop, gpu/decodev2/test_step.py:45-50)
+    from gpu.loop.generate import mma_decode
+
+    loop._graph = None
+    loop.reset()
+    seq = prompt + want[:6]
+    teacher = mr.teacher_logits(model, seq)
+    for i, tok in enumerate(seq):
+        loop.state.load_token(tok)
+        mma_decode(loop.state, loop.weights)
+        got = loop.state.arena.logits[0].float().cpu().numpy()
+        assert np.abs(got - teacher[i]).max() <= 0.05 * max(1.0, np.abs(teacher[i]).max())
+        top2 = np.sort(teacher[i])[-2:]
+        if top2[1] - top2[0] > 8 * 2.0 ** -8 * np.abs(teacher[i]).max():
+            assert int(loop.state.next_token.item()) == int(teacher[i].argmax())
 
 
 def test_host_seats_linear_and_embedding(golden):

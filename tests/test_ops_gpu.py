@@ -521,3 +521,74 @@ def test_prefill_row_kernels_match_the_torch_ops_bit_for_bit():
         assert torch.equal(y[r], row)
     ref = F.rms_norm(x.float(), (kdim,), w.float(), 1e-6)
     assert (y.float() - ref).abs().max() <= 2 ** -7 * ref.abs().max()
+
+
+GEMV_N_CASES = [
+    (2048, 2048, 2), (2560, 5120, 3), (1024, 5120, 8), (520, 13824, 4), (300, 27648, 8),
+    (6144, 6144, 4), (130, 65, 3), (333, 1000, 8), (64, 16384, 5), (7, 64, 1),
+]
+
+
+@pytest.mark.parametrize("m,k,n", GEMV_N_CASES)
+def test_gemv_n_matches_oracle_with_gemv_numerics(m, k, n):
+    """N activation rows against the float64 product with FP32-dequantized weights."""
+    from gpu.nf4 import nf4_gemv_n
+
+    rng = np.random.default_rng(m * 7 + k + n)
+    p, s, pt, st = blobs(m, k, m + k + n, weight_like=(m * k > 100000))
+    xt, xf = bf16_vec(rng, n, k)
+    bias_t, bias_f = bf16_vec(rng, m, std=0.1)
+    add_t, add_f = bf16_vec(rng, n, m, std=0.1)
+    w = o.dequantize(p, s, m, k).astype(np.float64)
+    y = nf4_gemv_n(pt, st, xt, m, k, o.padded_k(k))
+    assert y.shape == (n, m) and y.dtype is torch.bfloat16
+    assert_close(y, (xf.astype(np.float64) @ w.T).astype(np.float32), f"gemv_n {m}x{k} N={n}")
+    # bias + residual, written in place over the residual; and bit-stable on repeat
+    want = (xf.astype(np.float64) @ w.T + bias_f[None, :] + add_f).astype(np.float32)
+    buf = add_t.clone()
+    nf4_gemv_n(pt, st, xt, m, k, o.padded_k(k), out=buf, add=buf, bias=bias_t)
+    assert_close(buf, want, f"gemv_n+bias+add {m}x{k} N={n}")
+    buf2 = add_t.clone()
+    nf4_gemv_n(pt, st, xt, m, k, o.padded_k(k), out=buf2, add=buf2, bias=bias_t)
+    assert torch.equal(buf, buf2)
+
+
+def test_gemv_n_rows_are_independent_and_track_the_one_row_gemv():
+    from gpu.nf4 import nf4_gemv, nf4_gemv_n
+
+    m, k = 1536, 4096
+    rng = np.random.default_rng(3)
+    p, s, pt, st = blobs(m, k, 9)
+    xt, xf = bf16_vec(rng, 4, k)
+    y4 = nf4_gemv_n(pt, st, xt, m, k, k)
+    # a row does not depend on its neighbours (same row alone, or repeated, gives the same bits)
+    y1 = nf4_gemv_n(pt, st, xt[2:3].contiguous(), m, k, k)
+    assert torch.equal(y4[2], y1[0])
+    rep = nf4_gemv_n(pt, st, xt[1:2].repeat(8, 1).contiguous(), m, k, k)
+    assert all(torch.equal(rep[0], rep[i]) for i in range(8)) and torch.equal(rep[0], y4[1])
+    # and agrees with the one-row kernel to within the last bf16 place
+    g = nf4_gemv(pt, st, xt[0], m, k, k).view(-1).float()
+    d = (y4[0].float() - g).abs().max().item()
+    assert d <= 2.0 ** -7 * g.abs().max().item()
+    # NaN in one row of x stays in that row
+    bad = xt.clone()
+    bad[3, 17] = float("nan")
+    yb = nf4_gemv_n(pt, st, bad, m, k, k)
+    assert torch.equal(yb[:3], y4[:3]) and torch.isnan(yb[3].float()).all()
+
+
+def test_gemv_n_argument_errors():
+    from gpu.nf4 import _lib, nf4_gemv_n
+    from gpu.nf4._lib import ChrNf4Dev
+
+    p, s, pt, st = blobs(64, 27648, 1, weight_like=False)
+    xt = torch.zeros(9, 27648, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        nf4_gemv_n(pt, st, xt, 64, 27648, 27648)          # more than 8 rows
+    lib = _lib.load()
+    w = ChrNf4Dev(64, 27648, 27648, pt.data_ptr(), st.data_ptr())
+    assert lib.chr_nf4_gemv_n_ws(w, 8) == 5 * 8 * 64       # 27648 / 6144 -> 5 slices
+    y = torch.empty(8, 64, dtype=torch.bfloat16, device="cuda")
+    rc = lib.chr_nf4_gemv_n(w, xt.data_ptr(), y.data_ptr(), 8, None, None, None, 0, None)
+    assert rc == -7                                         # split-K workspace missing
+    assert lib.chr_nf4_gemv_n(w, xt.data_ptr(), y.data_ptr(), 9, None, None, None, 0, None) == -2
