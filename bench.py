@@ -292,7 +292,9 @@ def run_ours(args, spec) -> None:
         torch.cuda.empty_cache()
     spec = weights.spec
     if args.batch != 1:
-        raise SystemExit("--batch > 1 is not available in this build")
+        if world > 1:
+            raise SystemExit("--batch > 1 runs on one GPU")
+        return run_batched(args, spec, weights, local)
     loop = DecodeV2Loop.from_weights(weights, comm=comm)
     exchange = "none"
     if comm is not None:
@@ -334,8 +336,9 @@ def run_ours(args, spec) -> None:
         st = _lib.load().chr_nf4_gemv_status()
         if st != 0:
             raise SystemExit(f"{where}: GEMV status {st}")
-        if state.peers is not None and state.peers.timed_out():
-            raise SystemExit(f"{where}: a wait for a peer GPU ran out; the sums are not trustworthy")
+        for px in (state.peers, state.pick_peers):
+            if px is not None and px.timed_out():
+                raise SystemExit(f"{where}: a wait for a peer GPU ran out; the results are not trustworthy")
 
     # the first ids of the run, read once: the same at every N when tensor parallelism
     # is correct (and the same on every rank)
@@ -487,6 +490,88 @@ def run_ours(args, spec) -> None:
     if comm is not None:
         del step
         comm.shutdown(loop)
+
+
+def run_batched(args, spec, weights, local: int) -> None:
+    """``--batch B``: B sequences with a prompt each, decoded together (one graph per step)."""
+    import torch
+
+    from gpu.decodev2.batch import BatchLoop
+    from gpu.nf4 import _lib
+
+    b = args.batch
+    loop = BatchLoop(weights, b)
+    st = loop.state
+    prompts = [torch.randint(0, spec.vocab, (args.prompt,),
+                             generator=torch.Generator().manual_seed(2 + i)).tolist() for i in range(b)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    st.prefill(weights, prompts[:1] * b, chunk=args.chunk)        # untimed pass (lazy kernel loads)
+    torch.cuda.synchronize()
+    ev[0].record()
+    st.prefill(weights, prompts, chunk=args.chunk)
+    ev[1].record()
+    torch.cuda.synchronize()
+    prefill_ms = ev[0].elapsed_time(ev[1])
+    loop.capture_graph()
+    head_n = min(16, args.steps)
+    head = torch.zeros((head_n, b), dtype=torch.int64, device=st.device)
+    snap = [t.clone() for t in (st.token, st.position, st.valid_len)]
+    for i in range(head_n):
+        loop.step()
+        head[i].copy_(st.token)
+    torch.cuda.synchronize()
+    for t, s0 in zip((st.token, st.position, st.valid_len), snap):
+        t.copy_(s0)
+    for _ in range(args.warmup):
+        loop.step()
+    clocks = Clocks(local)
+    clocks.start()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        loop.step()
+    t1.record()
+    torch.cuda.synchronize()
+    dev_ms = t0.elapsed_time(t1)
+    host_tok = torch.zeros(b, dtype=torch.int64).pin_memory()
+    host_tok.copy_(st.token)
+    for t, s0 in zip((st.position, st.valid_len), snap[1:]):
+        t.copy_(s0)
+    stream = torch.cuda.current_stream()
+    w0 = time.perf_counter()
+    t0.record()
+    for _ in range(args.steps):
+        st.token.copy_(host_tok, non_blocking=True)
+        loop.step()
+        host_tok.copy_(st.token, non_blocking=True)
+        stream.synchronize()
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(t0.elapsed_time(t1), (time.perf_counter() - w0) * 1e3)
+    clk = clocks.stop()
+    if _lib.load().chr_nf4_gemv_status() != 0:
+        raise SystemExit("GEMV status word set")
+    peaks = measured_peaks()
+    step_bytes = spec.packed_bytes_per_token()
+    tokens = args.steps * b
+    path = "chr_nf4_gemv_n (CUDA cores, FP32 weights)" if b <= 8 else "chr_nf4_gemm_rows (tcgen05)"
+    line = {
+        "metric": f"decode_tok_s_bs{b}", "value": tokens / (dev_ms / 1e3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(spec, args),
+        "prefill_tok_s": b * args.prompt / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
+        "linears": path,
+        "step_hbm_gbs": step_bytes / (dev_ms / args.steps / 1e3) / 1e9,
+        "step_frac_of_hbm_peak": step_bytes / (dev_ms / args.steps / 1e3) / 1e9 / peaks["hbm"],
+        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": 8 * b,
+                "d2h_bytes_per_step": 8 * b},
+        "gpu_launches": args.steps * (1 + spec.n_layers * 10 + 2 + b),
+        "greedy_ids_head": [int(t) for t in head[:, 0].tolist()],
+        "clocks": clk,
+    }
+    print(json.dumps(line), flush=True)
 
 
 def main() -> None:

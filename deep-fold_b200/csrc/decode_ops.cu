@@ -212,6 +212,97 @@ pick_commit_kernel(const __nv_bfloat16 *__restrict__ logits, int n, int64_t *nex
   }
 }
 
+// The same pick when the logits are split over the ranks of a tensor-parallel group
+// (each rank holds a slice of the vocabulary): every rank finds its local best, the
+// last CTA pushes that one (key, index) pair into every peer's receive slots with plain
+// peer stores, raises a flag on each peer, waits (bounded) for the peers' flags, and
+// commits the best of all ranks. Two scalars per rank cross NVLink instead of the
+// logits. Epoch and status words as in the fused GEMV exchange.
+struct PickPeers {
+  int rank, world;
+  unsigned long long *keys[CHR_NF4_AR_MAX_RANKS];  // rank p's slots: [2 halves][world]
+  unsigned int *flags[CHR_NF4_AR_MAX_RANKS];       // rank p's flags: [world * CHR_NF4_AR_MAX_CTAS]
+  unsigned int *epoch;
+  int *status;
+  unsigned int polls;
+};
+
+__global__ void __launch_bounds__(kPickThreads)
+pick_commit_tp_kernel(const __nv_bfloat16 *__restrict__ logits, int n, int index_offset,
+                      const PickPeers pp, int64_t *next_token, int64_t *token, int64_t *position,
+                      uint8_t *finished, int64_t eos, unsigned long long *best,
+                      unsigned int *ticket) {
+  __shared__ unsigned long long red[kPickThreads / 32];
+  pdl_trigger();
+  pdl_wait();
+  unsigned long long key = 0ull;
+  const int stride = gridDim.x * kPickThreads;
+  for (int i = blockIdx.x * kPickThreads + threadIdx.x; i < n; i += stride) {
+    const unsigned long long cand = pick_key(__bfloat16_as_ushort(logits[i]), i + index_offset);
+    key = cand > key ? cand : key;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, key, off);
+    key = o > key ? o : key;
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = key;
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+#pragma unroll
+  for (int i = 1; i < kPickThreads / 32; ++i) key = red[i] > key ? red[i] : key;
+  atomicMax(best, key);
+  __threadfence();
+  if (atomicAdd(ticket, 1u) != gridDim.x - 1) return;
+  __threadfence();
+  unsigned long long win = atomicMax(best, 0ull);
+  *best = 0ull;
+  *ticket = 0u;
+  // exchange
+  const unsigned int e = *reinterpret_cast<volatile unsigned int *>(pp.epoch) + 1u;
+  const unsigned int half = (e & 1u) * static_cast<unsigned int>(pp.world);
+  for (int p = 0; p < pp.world; ++p) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(pp.keys[p] + half + pp.rank), "l"(win)
+                 : "memory");
+  }
+  __threadfence_system();
+  for (int p = 0; p < pp.world; ++p) {
+    if (p != pp.rank) {
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(pp.flags[p] + pp.rank * CHR_NF4_AR_MAX_CTAS),
+                   "r"(e)
+                   : "memory");
+    }
+  }
+  const bool give_up = *reinterpret_cast<volatile int *>(pp.status) != 0;
+  for (int r = 0; r < pp.world && !give_up; ++r) {
+    if (r == pp.rank) continue;
+    const unsigned int *f = pp.flags[pp.rank] + r * CHR_NF4_AR_MAX_CTAS;
+    unsigned int seen = 0, polls = 0;
+    for (;;) {
+      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+      if (static_cast<int>(seen - e) >= 0) break;
+      if (++polls >= pp.polls) {
+        atomicExch(pp.status, 1);
+        break;
+      }
+    }
+  }
+  __threadfence_system();
+  for (int r = 0; r < pp.world; ++r) {
+    unsigned long long other;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(other) : "l"(pp.keys[pp.rank] + half + r)
+                 : "memory");
+    win = other > win ? other : win;
+  }
+  const int64_t idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(win));
+  *next_token = idx;
+  if (token != nullptr) *token = idx;
+  if (position != nullptr) *position += 1;
+  if (finished != nullptr && idx == eos) *finished |= 1;
+  __threadfence();
+  *reinterpret_cast<volatile unsigned int *>(pp.epoch) = e;
+}
+
 }  // namespace
 }  // namespace chr
 
@@ -407,6 +498,47 @@ extern "C" int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_tok
       pick_commit_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kPickThreads), 0,
       static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16 *>(logits), n,
       static_cast<int64_t *>(next_token), static_cast<int64_t *>(token),
+      static_cast<int64_t *>(position), static_cast<uint8_t *>(finished), eos, best, ticket);
+  return e == cudaSuccess ? kOk : kLaunch;
+}
+
+extern "C" int chr_nf4_pick_commit_tp(const void *logits_local, int32_t n_local,
+                                      int32_t index_offset, const chr_nf4_peers_t *peers,
+                                      void *next_token, void *token, void *position,
+                                      void *finished, int64_t eos, void *scratch, void *stream) {
+  if (logits_local == nullptr || next_token == nullptr || scratch == nullptr || peers == nullptr) {
+    return kNull;
+  }
+  if (n_local < 1 || index_offset < 0) return kDims;
+  if (!aligned(scratch, 8)) return kAlign;
+  if (peers->world < 2 || peers->world > CHR_NF4_AR_MAX_RANKS || peers->rank < 0 ||
+      peers->rank >= peers->world) {
+    return kDims;
+  }
+  if (peers->epoch == nullptr || peers->status == nullptr) return kNull;
+  // the receive buffer holds 2 * world * capacity floats; the keys need 2 * world * 2
+  if (peers->capacity < 2) return kWorkspace;
+  PickPeers pp{};
+  pp.rank = peers->rank;
+  pp.world = peers->world;
+  pp.polls = peer_polls();
+  for (int p = 0; p < peers->world; ++p) {
+    if (peers->recv[p] == nullptr || peers->flags[p] == nullptr) return kNull;
+    if (!aligned(peers->recv[p], 8)) return kAlign;
+    pp.keys[p] = static_cast<unsigned long long *>(peers->recv[p]);
+    pp.flags[p] = static_cast<unsigned int *>(peers->flags[p]);
+  }
+  pp.epoch = static_cast<unsigned int *>(peers->epoch);
+  pp.status = static_cast<int *>(peers->status);
+  int blocks = (n_local + kPickThreads * 8 - 1) / (kPickThreads * 8);
+  const int sms = sm_count();
+  blocks = blocks < 1 ? 1 : (blocks > sms ? sms : blocks);
+  auto *best = static_cast<unsigned long long *>(scratch);
+  auto *ticket = reinterpret_cast<unsigned int *>(best + 1);
+  const cudaError_t e = launch_chain(
+      pick_commit_tp_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kPickThreads), 0,
+      static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16 *>(logits_local), n_local,
+      index_offset, pp, static_cast<int64_t *>(next_token), static_cast<int64_t *>(token),
       static_cast<int64_t *>(position), static_cast<uint8_t *>(finished), eos, best, ticket);
   return e == cudaSuccess ? kOk : kLaunch;
 }

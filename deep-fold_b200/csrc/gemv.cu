@@ -60,11 +60,6 @@ int launch(const GemvArgs &proto, cudaStream_t st) {
 // ---------------------------------------------------------------------------
 // Row-split GEMV with the cross-GPU sum fused in (see chr_nf4_gemv_allreduce).
 // ---------------------------------------------------------------------------
-constexpr unsigned int kPeerPolls = 1u << 22;
-unsigned int &peer_polls() {
-  static unsigned int v = kPeerPolls;
-  return v;
-}
 
 struct PeerArgs {
   int rank, world;
@@ -279,10 +274,6 @@ extern "C" int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu,
   out[4] = sh.n_tiles;
   out[5] = sh.grid;
   return kOk;
-}
-
-extern "C" void chr_nf4_set_peer_polls(uint32_t polls) {
-  peer_polls() = polls == 0 ? kPeerPolls : polls;
 }
 
 extern "C" int chr_nf4_gemv_status(void) {

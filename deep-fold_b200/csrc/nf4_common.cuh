@@ -59,6 +59,9 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 bool pdl_enabled();
 void set_pdl_enabled(bool on);
 
+constexpr unsigned int kPeerPollsDefault = 1u << 22;
+unsigned int &peer_polls();  // process-wide poll budget of the waits for a peer GPU
+
 // Launch with or without the programmatic attribute (process-wide switch).
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

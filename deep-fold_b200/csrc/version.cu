@@ -22,6 +22,16 @@ bool &pdl_flag() {
 }  // namespace
 bool pdl_enabled() { return pdl_flag(); }
 void set_pdl_enabled(bool on) { pdl_flag() = on; }
+
+// Poll budget of the waits for a peer GPU's flag (fused GEMV exchange, split pick).
+unsigned int &peer_polls() {
+  static unsigned int v = kPeerPollsDefault;
+  return v;
+}
 }  // namespace chr
+
+extern "C" void chr_nf4_set_peer_polls(uint32_t polls) {
+  chr::peer_polls() = polls == 0 ? chr::kPeerPollsDefault : polls;
+}
 
 extern "C" void chr_nf4_set_pdl(int32_t on) { chr::set_pdl_enabled(on != 0); }

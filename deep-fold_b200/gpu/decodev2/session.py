@@ -115,6 +115,15 @@ class DecodeV2Loop:
         teacher_force_token(self.state, self.weights, int(token_id))
 
     # ------------------------------------------------------------------- decode
+    def check_exchange(self) -> None:
+        """Raise if a bounded wait for a peer GPU ran out since the last check (tensor
+        parallel with the peer-memory exchange): the ids produced since then are not to
+        be trusted. One host read per exchange set; called after every decode window."""
+        for px in (self.state.peers, self.state.pick_peers):
+            if px is not None and px.timed_out():
+                raise RuntimeError("a wait for a peer GPU ran out of polls during decode; "
+                                   "the tensor-parallel sums since the last check are incomplete")
+
     def _step(self):
         return self._graph if self._graph is not None else greedy_decode
 
@@ -158,6 +167,7 @@ class DecodeV2Loop:
             seq += 1
         torch.cuda.synchronize()
         out.decode_ms = (time.perf_counter() - t1) * 1000.0
+        self.check_exchange()
         return out
 
     @torch.no_grad()
@@ -210,6 +220,7 @@ class DecodeV2Loop:
         out.prefill_ms = ev[0].elapsed_time(ev[1])
         out.decode_ms = ev[2].elapsed_time(ev[3])
         out.decode_steps = limit - 1
+        self.check_exchange()
         return out
 
     # ------------------------------------------------------------ warm-up/graph

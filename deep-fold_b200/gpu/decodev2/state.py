@@ -136,6 +136,7 @@ class DecodeState:
     eos_id: torch.Tensor
     comm: object = None          # tp.Comm; None = single GPU
     peers: object = None         # tp.PeerExchange: row-split sums over peer memory instead of NCCL
+    pick_peers: object = None    # tp.PeerExchange of the greedy pick (a set of its own)
 
     def enable_peer_exchange(self, on: bool = True) -> str | None:
         """Sum the row-split partials inside the GEMV launch, over NVLink peer memory
@@ -143,11 +144,14 @@ class DecodeState:
         were mapped, or ``None`` when switched off / single GPU."""
         if not on or self.comm is None or self.comm.world < 2:
             self.peers = None
+            self.pick_peers = None
             return None
         if self.peers is None:
             from .tp import PeerExchange
 
             self.peers = PeerExchange(self.comm, self.spec.hidden, self.device)
+            # the pick's (value, id) pairs travel through a small set of their own
+            self.pick_peers = PeerExchange(self.comm, 2, self.device)
         return self.peers.how
 
     @classmethod

@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 from gpu.nf4 import (ATTN_SPLIT, nf4_attn, nf4_gemv, nf4_gemv_allreduce, nf4_gemv_f32,
-                     nf4_pick_commit, nf4_qkv, nf4_rms, nf4_swiglu)
+                     nf4_pick_commit, nf4_pick_commit_tp, nf4_qkv, nf4_rms, nf4_swiglu)
 
 from .embed import PackedEmbed
 from .linear import DeviceLayer, DeviceLinear, DeviceWeights
@@ -93,7 +93,9 @@ def _accumulate(state: DecodeState, mat: DeviceLinear, src: torch.Tensor, dest: 
     dest.view(-1).add_(part)
 
 
-def forward_decode(state: DecodeState, weights: DeviceWeights) -> None:
+def forward_decode(state: DecodeState, weights: DeviceWeights, *, gather_logits: bool = True) -> None:
+    """``gather_logits=False`` (tensor parallel only) leaves each rank with its slice in
+    ``arena.logits_local``: the greedy pick then exchanges one pair per rank instead."""
     spec, ar = state.spec, state.arena
     _embed_into(state, weights)
     for li, layer in enumerate(weights.layers):
@@ -114,11 +116,19 @@ def forward_decode(state: DecodeState, weights: DeviceWeights) -> None:
     else:  # vocabulary slice per rank, gathered in rank order into the full logits
         nf4_gemv(head.packed, head.scale, x, head.M, head.K, head.K_pad,
                  ar.logits_local.view(-1), head.bias, rms_w, spec.rms_eps)
-        state.comm.all_gather_into(ar.logits.view(-1), ar.logits_local.view(-1))
+        if gather_logits:
+            state.comm.all_gather_into(ar.logits.view(-1), ar.logits_local.view(-1))
 
 
 def greedy_decode(state: DecodeState, weights: DeviceWeights) -> None:
     """Forward + pick + commit: ``token``/``position``/``finished`` advance on the device."""
+    if state.spec.tp > 1 and state.pick_peers is not None:
+        forward_decode(state, weights, gather_logits=False)
+        local = state.arena.logits_local.view(-1)
+        nf4_pick_commit_tp(local, state.comm.rank * local.numel(), state.pick_peers.peers,
+                           state.next_token, state.arena.pick_scratch, state.token, state.position,
+                           state.finished, int(state.spec.eos_id))
+        return
     forward_decode(state, weights)
     nf4_pick_commit(state.arena.logits.view(-1), state.next_token, state.arena.pick_scratch,
                     state.token, state.position, state.finished, int(state.spec.eos_id))

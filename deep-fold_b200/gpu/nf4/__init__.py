@@ -37,6 +37,7 @@ __all__ = [
     "nf4_attn_batch",
     "GEMV_MAX_N",
     "nf4_pick_commit",
+    "nf4_pick_commit_tp",
     "nf4_plan",
     "nf4_qkv",
     "nf4_rms",
@@ -738,6 +739,28 @@ def _rows_view(t: torch.Tensor, what: str) -> tuple[int, int]:
     if not t.is_cuda or t.dtype is not torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
         _fail(f"{what} must be a CUDA bfloat16 [N, F] view with contiguous rows")
     return int(t.size(0)), int(t.stride(0))
+
+
+def nf4_pick_commit_tp(
+    logits_local: torch.Tensor,
+    index_offset: int,
+    peers,
+    next_token: torch.Tensor,
+    scratch: torch.Tensor,
+    token: torch.Tensor | None = None,
+    position: torch.Tensor | None = None,
+    finished: torch.Tensor | None = None,
+    eos: int = -1,
+) -> None:
+    """Greedy pick over a vocabulary split across ranks: local argmax, one (value, id) pair
+    exchanged per rank over peer memory, the same commit on every rank."""
+    if not logits_local.is_cuda or logits_local.dtype is not torch.bfloat16 or not logits_local.is_contiguous():
+        _fail("logits_local must be contiguous CUDA bf16")
+    rc = _lib.load().chr_nf4_pick_commit_tp(
+        _ptr(logits_local), int(logits_local.numel()), int(index_offset), ctypes.byref(peers),
+        _ptr(next_token), _ptr(token), _ptr(position), _ptr(finished), int(eos), _ptr(scratch),
+        _stream())
+    _lib.check(rc, "chr_nf4_pick_commit_tp")
 
 
 def nf4_rms_rows(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:

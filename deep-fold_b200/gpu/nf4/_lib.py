@@ -127,6 +127,11 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     ),
+    "chr_nf4_pick_commit_tp": (
+        c_int,
+        [c_void_p, c_int32, c_int32, POINTER(ChrNf4Peers), c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int64, c_void_p, c_void_p],
+    ),
     "chr_nf4_rms_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_int32, c_float,
                                  c_void_p]),
     "chr_nf4_rope_kv_rows": (

@@ -273,6 +273,19 @@ int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_token,
                         void *token, void *position, void *finished,
                         int64_t eos, void *scratch, void *stream);
 
+/* chr_nf4_pick_commit when the logits are split over a tensor-parallel group: this rank
+ * holds logits_local[0..n_local) = vocabulary ids index_offset..index_offset+n_local-1.
+ * Each rank picks its local best, exchanges that one (value, id) pair with every peer
+ * over the mapped buffers of `peers` (plain peer stores + a flag per peer, bounded wait,
+ * sticky status word, as chr_nf4_gemv_allreduce) and all ranks commit the same global
+ * argmax: two scalars per rank cross NVLink instead of the logits. The peers struct
+ * must be a set of its own (its epoch advances once per call); capacity >= 2.
+ * No counterpart in the reference (single GPU). */
+int chr_nf4_pick_commit_tp(const void *logits_local, int32_t n_local, int32_t index_offset,
+                           const chr_nf4_peers_t *peers, void *next_token, void *token,
+                           void *position, void *finished, int64_t eos, void *scratch,
+                           void *stream);
+
 /* chr_nf4_attn without the workspace argument, for callers that have no way to
  * allocate device memory (a pointer-forwarding binding, a plugin without access
  * to the host's memory pool, code under a no-allocation rule). No counterpart in

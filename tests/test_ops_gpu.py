@@ -592,3 +592,60 @@ def test_gemv_n_argument_errors():
     rc = lib.chr_nf4_gemv_n(w, xt.data_ptr(), y.data_ptr(), 8, None, None, None, 0, None)
     assert rc == -7                                         # split-K workspace missing
     assert lib.chr_nf4_gemv_n(w, xt.data_ptr(), y.data_ptr(), 9, None, None, None, 0, None) == -2
+
+
+def test_peer_waits_run_out_and_report_instead_of_hanging():
+    """One GPU plays rank 0 of a 2-rank group whose peer never raises its flags: the fused
+    GEMV exchange and the split pick both return after their (shortened) poll budget with the
+    status word set, and later calls skip the wait until the host clears it."""
+    from gpu.nf4 import _lib, nf4_gemv_allreduce, nf4_pick_commit_tp
+    from gpu.nf4._lib import AR_MAX_CTAS, ChrNf4Peers
+
+    lib = _lib.load()
+    m, k = 512, 2048
+    rng = np.random.default_rng(11)
+    p, s, pt, st = blobs(m, k, 4)
+    xt, xf = bf16_vec(rng, k)
+
+    def peers_for(capacity):
+        bufs = [torch.zeros(2 * 2 * capacity + 2 * AR_MAX_CTAS, dtype=torch.float32, device="cuda")
+                for _ in range(2)]
+        epoch = torch.zeros(2, dtype=torch.int32, device="cuda")
+        status = torch.zeros((), dtype=torch.int32, device="cuda")
+        pr = ChrNf4Peers()
+        pr.rank, pr.world, pr.capacity = 0, 2, capacity
+        for r, b in enumerate(bufs):
+            pr.recv[r] = b.data_ptr()
+            pr.flags[r] = b.data_ptr() + 4 * 2 * 2 * capacity
+        pr.epoch, pr.status = epoch.data_ptr(), status.data_ptr()
+        return pr, (bufs, epoch, status)
+
+    lib.chr_nf4_set_peer_polls(2000)
+    try:
+        pr, keep = peers_for(m)
+        y = torch.zeros(m, dtype=torch.bfloat16, device="cuda")
+        nf4_gemv_allreduce(pt, st, xt, m, k, k, y, pr)
+        torch.cuda.synchronize()
+        assert int(keep[2].item()) == 1                       # the wait ran out and said so
+        # the sum holds this rank's partial (the absent peer's slot is still zero)
+        want = o.dequantize(p, s, m, k).astype(np.float64) @ xf.astype(np.float64)
+        assert_close(y.reshape(m, 1), want.astype(np.float32).reshape(m, 1), "partial after a timed-out wait")
+        nf4_gemv_allreduce(pt, st, xt, m, k, k, y, pr)        # sticky status: no second wait
+        torch.cuda.synchronize()
+        assert int(keep[2].item()) == 1 and int(keep[1][0].item()) == 2
+        # capacity is enforced
+        small, keep2 = peers_for(m - 1)
+        with pytest.raises(RuntimeError, match=r"\(-7\)"):
+            nf4_gemv_allreduce(pt, st, xt, m, k, k, y, small)
+        # split pick
+        pk, keep3 = peers_for(2)
+        logits = torch.randn(4096, device="cuda").to(torch.bfloat16)
+        nxt = torch.zeros((), dtype=torch.int64, device="cuda")
+        scratch = torch.zeros(16, dtype=torch.uint8, device="cuda")
+        nf4_pick_commit_tp(logits, 4096, pk, nxt, scratch)
+        torch.cuda.synchronize()
+        assert int(keep3[2].item()) == 1
+        assert int(nxt.item()) == 4096 + int(logits.float().argmax().item())
+    finally:
+        lib.chr_nf4_set_peer_polls(0)
+    assert lib.chr_nf4_gemv_status() == 0
