@@ -442,6 +442,37 @@ def run_ours(args, spec) -> None:
                      "shape": [gu[0].M, gu[0].K, n_tok], "us_per_launch": g_ms * 1e3, "traffic": None}
         del xin, yout
 
+    # where the step's time goes: every operation kind swept over all layers as its own
+    # captured graph (collective under tensor parallelism: all ranks run the same sweeps)
+    breakdown = None
+    if args.breakdown:
+        from gpu.decodev2 import step as stepmod
+        from gpu.nf4 import ATTN_SPLIT, nf4_attn
+
+        def per_layer(fn):
+            def run():
+                for li, ly in enumerate(layers):
+                    fn(li, ly)
+            return graph_timed(run, 3, torch) * 1e3 / len(layers)
+
+        state.position.copy_(snap["position"])
+        state.valid_len.copy_(snap["valid_len"])
+        head = weights.lm_head
+        breakdown = {
+            "qkv": per_layer(lambda li, ly: stepmod._qkv(state, ly)),
+            "attention": per_layer(lambda li, ly: nf4_attn(
+                ar.q, state.kv.k[li], state.kv.v[li], ar.attn, state.valid_len, spec.attn_scale,
+                ar.attn_ws, ATTN_SPLIT, ar.k, ar.v, state.cos, state.sin, state.position)),
+            "o_proj(+exchange)": per_layer(lambda li, ly: stepmod._accumulate(state, ly.o, ar.attn, ar.x)),
+            "gate_up_swiglu": k_us,
+            "down_proj(+exchange)": per_layer(
+                lambda li, ly: stepmod._accumulate(state, ly.down, ar.down_in, ar.x)),
+        }
+        breakdown["per_layer_sum"] = sum(breakdown.values())
+        breakdown["layers_ms"] = breakdown["per_layer_sum"] * len(layers) / 1e3
+        breakdown["unit"] = "us per launch (layers_ms: all layers, ms)"
+        check_status("after the breakdown sweeps")
+
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local}")
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -481,6 +512,8 @@ def run_ours(args, spec) -> None:
                                           "algorithmic bytes"}
     if gemm_roof is not None:
         line["gemm_roofline"] = gemm_roof
+    if breakdown is not None:
+        line["step_breakdown"] = breakdown
     line["step_mode"] = "launch chain in one CUDA graph"
     line["row_split_exchange"] = exchange
     line["prefill_mode"] = prefill_mode
@@ -586,6 +619,8 @@ def main() -> None:
     ap.add_argument("--chunk", type=int, default=512, help="prefill chunk width")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="also time every operation kind of the step on its own (per-layer sweeps)")
     ap.add_argument("--prefill-graphs", action="store_true",
                     help="replay the prefill chunks as captured graphs instead of issuing them from Python")
     ap.add_argument("--nccl", action="store_true",

@@ -78,10 +78,46 @@ __global__ void rope_kv_kernel(__nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__r
 // overlap on the device (different streams) would share them and must not.
 __device__ unsigned int g_attn_arrivals[kMaxAttnGroups];
 
+// The item's shared memory is dynamic (above 48 KB for head dims over 64): the limit
+// of each kernel is raised once per device, before its first launch.
+template <int P, int H, typename Kernel>
+static bool attn_smem_ready(Kernel kernel) {
+  static int done[64] = {};
+  return ensure_smem_attr(kernel, static_cast<int>(sizeof(AttnSmem<P, H>)), done);
+}
+
+// Query heads one item serves: the group size when a kernel is built for it, else
+// the next size up (the spare heads carry zero queries); groups above 8 heads (4 for
+// head dims over 128) are cut into chunks.
+static int attn_heads_per_item(int n_rep, int hd) {
+  const int cap = hd <= 128 ? 8 : 4;
+  if (n_rep >= cap) return cap;
+  if (n_rep <= 2) return n_rep;
+  if (n_rep <= 4) return 4;
+  return n_rep == 5 ? 5 : 8;
+}
+static int attn_head_chunks(int n_rep, int hd) {
+  const int heads = attn_heads_per_item(n_rep, hd);
+  return (n_rep + heads - 1) / heads;
+}
+// Splits of the sequence actually used: the caller's count, at most kAttnMaxSplit,
+// halved while the grid (splits x groups, one 512-thread CTA per SM) would not fit
+// the device in one wave. A second wave costs more than longer rows per warp save.
+static int attn_splits_used(int n_split, long long groups) {
+  int s = n_split > kAttnMaxSplit ? kAttnMaxSplit : n_split;
+  const long long sms = sm_count();
+  while (s > 1 && s * groups > sms) s = (s + 1) / 2;
+  return s;
+}
+#define CHR_ATTN_SHAPES(X)                                                                     \
+  X(1, 1) X(1, 2) X(1, 4) X(1, 5) X(1, 8) X(2, 1) X(2, 2) X(2, 4) X(2, 5) X(2, 8) X(4, 1)      \
+  X(4, 2) X(4, 4)
+
 // Grid: (splits, kv heads, head chunks); the core is in attn_core.cuh.
 template <int P, int H>
-__global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const AttnArgs a) {
-  __shared__ AttnSmem<P, H> sm;
+__global__ void __launch_bounds__(kAttnThreads, 1) attn_split_kernel(const AttnArgs a) {
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  AttnSmem<P, H> &sm = *reinterpret_cast<AttnSmem<P, H> *>(attn_smem);
   pdl_trigger();
   pdl_wait();  // q, k_act, v_act, position and valid_len come from earlier kernels
   unsigned int *ctr = &g_attn_arrivals[(blockIdx.y * gridDim.z + blockIdx.z) % kMaxAttnGroups];
@@ -98,9 +134,10 @@ struct AttnBatch {
 };
 
 template <int P, int H>
-__global__ void __launch_bounds__(kAttnThreads) attn_batch_kernel(const AttnArgs proto,
+__global__ void __launch_bounds__(kAttnThreads, 1) attn_batch_kernel(const AttnArgs proto,
                                                                  const AttnBatch bt) {
-  __shared__ AttnSmem<P, H> sm;
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  AttnSmem<P, H> &sm = *reinterpret_cast<AttnSmem<P, H> *>(attn_smem);
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.y / proto.n_kv;
@@ -352,12 +389,10 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
     return kDims;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // The workspace is sized for the caller's n_split; at most 16 splits are used
-  // (8 warps per CTA keep the same number of rows in flight), which halves the
-  // partials the merging CTA has to read back.
-  if (n_split > kAttnMaxSplit) n_split = kAttnMaxSplit;
-  const int slots = n_q * n_split;
+  // The workspace is sized for the caller's n_split; fewer splits may be used.
   const int n_rep = n_q / n_kv;
+  n_split = attn_splits_used(n_split, n_kv * attn_head_chunks(n_rep, hd));
+  const int slots = n_q * n_split;
   AttnArgs a{};
   a.q = static_cast<const __nv_bfloat16 *>(q);
   a.q_group_stride = n_rep * hd;
@@ -381,22 +416,21 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
   a.max_seq = max_seq;
   a.scale = scale;
 
+  const int heads = attn_heads_per_item(n_rep, hd);
+  const int head_chunks = (n_rep + heads - 1) / heads;
+  if (n_kv * head_chunks > kMaxAttnGroups) return kDims;
+  const dim3 grid(static_cast<unsigned>(n_split), static_cast<unsigned>(n_kv),
+                  static_cast<unsigned>(head_chunks));
+  cudaError_t e = cudaErrorInvalidValue;
 #define CHR_ATTN(PP, HH)                                                                       \
-  launch_chain(attn_split_kernel<PP, HH>,                                                      \
-               dim3(static_cast<unsigned>(n_split), static_cast<unsigned>(n_kv),               \
-                    static_cast<unsigned>((n_rep + HH - 1) / HH)),                             \
-               dim3(kAttnThreads), 0, st, a)
-  cudaError_t e;
-  if (hd <= 64) {
-    if (n_kv * ((n_rep + 7) / 8) > kMaxAttnGroups) return kDims;
-    e = CHR_ATTN(1, 8);
-  } else if (hd <= 128) {
-    if (n_kv * ((n_rep + 7) / 8) > kMaxAttnGroups) return kDims;
-    e = CHR_ATTN(2, 8);
-  } else {
-    if (n_kv * ((n_rep + 3) / 4) > kMaxAttnGroups) return kDims;
-    e = CHR_ATTN(4, 4);
+  if (pieces == PP && heads == HH) {                                                           \
+    if (attn_smem_ready<PP, HH>(attn_split_kernel<PP, HH>)) {                                  \
+      e = launch_chain(attn_split_kernel<PP, HH>, grid, dim3(kAttnThreads),                    \
+                       sizeof(AttnSmem<PP, HH>), st, a);                                       \
+    }                                                                                          \
   }
+  const int pieces = hd <= 64 ? 1 : (hd <= 128 ? 2 : 4);
+  CHR_ATTN_SHAPES(CHR_ATTN)
 #undef CHR_ATTN
   return e == cudaSuccess ? kOk : kLaunch;
 }
@@ -416,9 +450,9 @@ extern "C" int chr_nf4_attn_batch(const void *q, const void *k, const void *v, v
     return kDims;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (n_split > kAttnMaxSplit) n_split = kAttnMaxSplit;
-  const int slots = n_q * n_split;
   const int n_rep = n_q / n_kv;
+  n_split = attn_splits_used(n_split, batch * n_kv * attn_head_chunks(n_rep, hd));
+  const int slots = n_q * n_split;
   AttnArgs a{};
   a.q = static_cast<const __nv_bfloat16 *>(q);
   a.q_group_stride = n_rep * hd;
@@ -448,19 +482,22 @@ extern "C" int chr_nf4_attn_batch(const void *q, const void *k, const void *v, v
   bt.cache_stride = static_cast<long long>(max_seq) * n_kv * hd;
   bt.out_stride = static_cast<long long>(n_q) * hd;
   bt.ws_stride = static_cast<long long>(slots) * (hd + 2);
-  const int heads_per_item = hd <= 128 ? 8 : 4;
-  const int chunks = (n_rep + heads_per_item - 1) / heads_per_item;
+  const int heads = attn_heads_per_item(n_rep, hd);
+  const int chunks = (n_rep + heads - 1) / heads;
   if (static_cast<long long>(batch) * n_kv * chunks > kMaxAttnGroups) return kDims;
   const dim3 grid(static_cast<unsigned>(n_split), static_cast<unsigned>(batch * n_kv),
                   static_cast<unsigned>(chunks));
-  cudaError_t e;
-  if (hd <= 64) {
-    e = launch_chain(attn_batch_kernel<1, 8>, grid, dim3(kAttnThreads), 0, st, a, bt);
-  } else if (hd <= 128) {
-    e = launch_chain(attn_batch_kernel<2, 8>, grid, dim3(kAttnThreads), 0, st, a, bt);
-  } else {
-    e = launch_chain(attn_batch_kernel<4, 4>, grid, dim3(kAttnThreads), 0, st, a, bt);
+  cudaError_t e = cudaErrorInvalidValue;
+#define CHR_ATTN_B(PP, HH)                                                                     \
+  if (pieces == PP && heads == HH) {                                                           \
+    if (attn_smem_ready<PP, HH>(attn_batch_kernel<PP, HH>)) {                                  \
+      e = launch_chain(attn_batch_kernel<PP, HH>, grid, dim3(kAttnThreads),                    \
+                       sizeof(AttnSmem<PP, HH>), st, a, bt);                                   \
+    }                                                                                          \
   }
+  const int pieces = hd <= 64 ? 1 : (hd <= 128 ? 2 : 4);
+  CHR_ATTN_SHAPES(CHR_ATTN_B)
+#undef CHR_ATTN_B
   return e == cudaSuccess ? kOk : kLaunch;
 }
 

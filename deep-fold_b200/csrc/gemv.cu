@@ -71,6 +71,12 @@ struct PeerArgs {
   unsigned int polls;
 };
 
+// Exchange protocol: every 8-byte store to a peer carries one FP32 partial and the
+// call's epoch, so a row needs neither a fence nor a separate flag: the receiver polls
+// the word itself until the epoch matches (one NVLink trip instead of store + system
+// fence + flag + poll). Each rank's receive buffer holds, per half (calls alternate
+// between two halves) and per source rank, `capacity` such words; a rank keeps its own
+// partial as plain floats in its own slot of its own buffer.
 template <int V, int R, int C>
 __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
 nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
@@ -85,82 +91,68 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
   // (kept in the ring header of the dynamic allocation: the kernels of this family
   // declare no static shared memory, their layout counts on it)
   const uint32_t epoch_slot = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + 144u;
+  auto slot_of = [&](int owner, unsigned int e, int source) -> uint2 * {
+    return reinterpret_cast<uint2 *>(pa.recv[owner]) +
+           (static_cast<size_t>(e & 1u) * pa.world + source) * pa.capacity;
+  };
   GemvArgs b = a;
-  // Every thread passes the same y32: this rank's own slot of the current half.
-  // The half depends on the epoch, which is only known after the dependency wait;
-  // gemv_run reads b.y32 after wait() returns.
+  // Every thread passes the same y32: this rank's own slot of the current half. It
+  // depends on the epoch, which is only known after the dependency wait; gemv_run reads
+  // b.y32 after wait() returns.
   gemv_run<V, R, C, 0>(b, smem, blockIdx.x, gridDim.x, [&] {
     pdl_wait();  // x and the residual belong to the previous kernel until it ends
     const unsigned int e = *reinterpret_cast<volatile unsigned int *>(pa.epoch) + 1u;
-    const size_t half = static_cast<size_t>(e & 1u) * pa.world * pa.capacity;
-    b.y32 = pa.recv[pa.rank] + half + static_cast<size_t>(pa.rank) * pa.capacity;
+    b.y32 = reinterpret_cast<float *>(slot_of(pa.rank, e, pa.rank));
     if (tid == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(epoch_slot), "r"(e) : "memory");
   });
   __syncthreads();  // this CTA's rows are stored (by its helper warp or its workers)
   unsigned int e;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(epoch_slot) : "memory");
-  const size_t half = static_cast<size_t>(e & 1u) * pa.world * pa.capacity;
-  float *mine = pa.recv[pa.rank] + half + static_cast<size_t>(pa.rank) * pa.capacity;
+  const float *mine = reinterpret_cast<const float *>(slot_of(pa.rank, e, pa.rank));
+  // a wait that ran out earlier (status is sticky until the host clears it) means a
+  // peer is gone: do not spend the full poll budget again on every call
+  const bool give_up = *reinterpret_cast<volatile int *>(pa.status) != 0;
 
   // Rows of this CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of G*R rows.
   const int rt = a.G * R;
-  // 1. push them into every peer's slot for this rank
-  for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
-    for (int u = tid; u < rt; u += blockDim.x) {
-      const int row = tile * rt + u;
-      if (row < M) {
-        const float v = __ldcg(mine + row);
-        for (int p = 0; p < pa.world; ++p) {
-          if (p != pa.rank) pa.recv[p][half + static_cast<size_t>(pa.rank) * pa.capacity + row] = v;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  // 2. tell the peers' namesake CTAs, then wait for theirs
-  const unsigned int slot = static_cast<unsigned int>(pa.rank) * CHR_NF4_AR_MAX_CTAS + blockIdx.x;
-  if (tid == 0) {
-    __threadfence_system();
-    for (int p = 0; p < pa.world; ++p) {
-      if (p != pa.rank) {
-        // the fence above is the release; the flag itself is a relaxed store
-        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(pa.flags[p] + slot), "r"(e)
-                     : "memory");
-      }
-    }
-  }
-  if (tid < pa.world && tid != pa.rank) {
-    const unsigned int *f = pa.flags[pa.rank] + static_cast<unsigned int>(tid) * CHR_NF4_AR_MAX_CTAS +
-                            blockIdx.x;
-    unsigned int seen = 0, polls = 0;
-    // a wait that ran out earlier (status is sticky until the host clears it) means a
-    // peer is gone: do not spend the full poll budget again on every call
-    const bool give_up = *reinterpret_cast<volatile int *>(pa.status) != 0;
-    for (; !give_up;) {
-      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
-      // epochs only grow; the difference form survives the 32-bit wrap
-      if (static_cast<int>(seen - e) >= 0) break;
-      if (++polls >= pa.polls) {
-        atomicExch(pa.status, 1);
-        break;
-      }
-    }
-    __threadfence_system();
-  }
-  __syncthreads();
-  // 3. sum in rank order, add the residual, round once
   __nv_bfloat16 *y = a.y[0];
   for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
     for (int u = tid; u < rt; u += blockDim.x) {
       const int row = tile * rt + u;
-      if (row < M) {
-        float v = 0.f;
-        for (int r = 0; r < pa.world; ++r) {
-          v += __ldcg(pa.recv[pa.rank] + half + static_cast<size_t>(r) * pa.capacity + row);
+      if (row >= M) continue;
+      const float own = __ldcg(mine + row);
+      // 1. push (value, epoch) into every peer's slot for this rank
+      for (int p = 0; p < pa.world; ++p) {
+        if (p != pa.rank) {
+          asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(slot_of(p, e, pa.rank) + row),
+                       "r"(__float_as_uint(own)), "r"(e)
+                       : "memory");
         }
-        v += __bfloat162float(y[row]);
-        y[row] = __float2bfloat16(v);
       }
+      // 2. collect the peers' words for the same row, summing in rank order
+      float v = 0.f;
+      for (int r = 0; r < pa.world; ++r) {
+        if (r == pa.rank) {
+          v += own;
+          continue;
+        }
+        const uint2 *src = slot_of(pa.rank, e, r) + row;
+        uint32_t bits = 0u, seen = 0u;
+        unsigned int polls = 0;
+        for (;;) {
+          asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(seen) : "l"(src)
+                       : "memory");
+          if (seen == e || give_up) break;
+          if (++polls >= pa.polls) {
+            atomicExch(pa.status, 1);
+            break;
+          }
+        }
+        v += seen == e ? __uint_as_float(bits) : 0.f;
+      }
+      // 3. add the residual, round once
+      v += __bfloat162float(y[row]);
+      y[row] = __float2bfloat16(v);
     }
   }
   // 4. the last CTA out publishes the new epoch

@@ -910,19 +910,6 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) nf4_gemv_kernel(const
   });
 }
 
-// Set the dynamic shared-memory limit of a kernel once per device.
-template <typename Kernel>
-inline bool ensure_smem_attr(Kernel kernel, int bytes, int (&done)[64]) {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-  if (done[dev] >= bytes) return true;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
-    return false;
-  }
-  done[dev] = bytes;
-  return true;
-}
-
 template <int V, int MODE>
 inline int launch_gemv(const GemvArgs &proto, const GemvShape &sh, cudaStream_t st) {
   GemvArgs a = proto;

@@ -79,6 +79,19 @@ inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block,
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Set the dynamic shared-memory limit of a kernel once per device.
+template <typename Kernel>
+inline bool ensure_smem_attr(Kernel kernel, int bytes, int (&done)[64]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  if (done[dev] >= bytes) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    return false;
+  }
+  done[dev] = bytes;
+  return true;
+}
+
 inline int sm_count() {
   static int cached = 0;
   if (cached > 0) return cached;

@@ -60,7 +60,7 @@ class BatchState:
         self.k_act, self.v_act = z(spec.n_kv, spec.head_dim), z(spec.n_kv, spec.head_dim)
         self.attn = z(spec.q_dim)
         self.logits = z(spec.vocab)
-        self.attn_ws = torch.zeros(b * spec.n_q * 16 * (spec.head_dim + 2), dtype=torch.float32,
+        self.attn_ws = torch.zeros(b * spec.n_q * ATTN_SPLIT * (spec.head_dim + 2), dtype=torch.float32,
                                    device=dev)
         self.pick_scratch = torch.zeros((b, 16), dtype=torch.uint8, device=dev)
         self.status = torch.zeros((), dtype=torch.int32, device=dev)

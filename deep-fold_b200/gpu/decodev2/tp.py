@@ -108,8 +108,8 @@ class Comm:
 class PeerExchange:
     """Buffers of the fused row-split GEMV + all-reduce (``chr_nf4_gemv_allreduce``).
 
-    Every rank allocates a receive buffer (two epochs x one slot per source rank x
-    ``max_rows`` floats) and a block of flag words in memory that all ranks of the box
+    Every rank allocates a receive buffer (two halves x one slot per source rank x
+    ``max_rows`` 8-byte words of (value, epoch)) and a block of flag words in memory that all ranks of the box
     can address, exchanges the mappings once, and keeps the ``chr_nf4_peers_t`` the
     kernel takes. Mapping goes through torch's symmetric memory (NVLink peer access,
     multicast left off); when that is unavailable, through CUDA IPC handles of ordinary
@@ -128,7 +128,7 @@ class PeerExchange:
         self.comm, self.max_rows = comm, int(max_rows)
         self._per_shape: dict = {}
         dev = torch.device(device)
-        n_recv = 2 * comm.world * self.max_rows              # float32
+        n_recv = 2 * comm.world * self.max_rows * 2          # two halves x ranks x rows of 8-byte words
         n_flags = comm.world * AR_MAX_CTAS                   # uint32, kept as int32
         n_words = n_recv + n_flags
         self.how = "symmetric_memory"

@@ -566,7 +566,7 @@ def nf4_attn_batch(
     n_split = int(n_split)
     if not 1 <= n_split <= 64:
         _fail("n_split must be 1..64")
-    if ws.dtype is not torch.float32 or not ws.is_cuda or ws.numel() < b * n_q * min(n_split, 16) * (hd + 2):
+    if ws.dtype is not torch.float32 or not ws.is_cuda or ws.numel() < b * n_q * min(n_split, 32) * (hd + 2):
         _fail("attn workspace too small")
     rc = _lib.load().chr_nf4_attn_batch(
         _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(valid_len), _ptr(ws), b, n_q, n_kv, hd, n_split,

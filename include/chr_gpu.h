@@ -112,7 +112,8 @@ int chr_nf4_rope_kv(void *q, void *k, const void *v, void *k_cache, void *v_cach
  * position (device int64) q is rotated in FP32; with k_act/v_act as well, the
  * rotated current k and the current v are written to cache row *position and
  * the current token is attended with those unrounded FP32 values.
- * hd <= 256, hd % 8 == 0, n_split in [1, 64] (at most 16 splits are used).
+ * hd <= 256, hd % 8 == 0, n_split in [1, 64] (at most 32 splits are used, and fewer while splits x kv heads
+ * x head chunks would exceed the SM count; the workspace is sized for n_split).
  * Cross-call state: the splits of a kv head are merged by the last CTA to arrive,
  * counted in a small array inside the library that every call leaves zeroed. Calls
  * that follow each other on one stream (or are otherwise ordered) are fine; two
@@ -128,7 +129,7 @@ int chr_nf4_attn(const void *q, const void *k, const void *v, void *out,
 /* chr_nf4_attn for `batch` independent sequences in one launch (batched decode):
  * q [batch, n_q, hd], k_act / v_act [batch, n_kv, hd], k / v caches
  * [batch, max_seq, n_kv, hd], out [batch, n_q*hd], valid_len int32 [batch],
- * position int64 [batch], ws batch * n_q*min(n_split,16)*(hd+2) floats; cos / sin
+ * position int64 [batch], ws batch * n_q*min(n_split,32)*(hd+2) floats; cos / sin
  * are shared. batch * n_kv * ceil(n_rep / 8) must not exceed 1024 (-3). Same
  * arithmetic per sequence as chr_nf4_attn. No counterpart in the reference, whose
  * decode is one sequence (gpu/nf4/nf4_gemv.cu:599-727). */
@@ -179,23 +180,26 @@ int chr_nf4_gemv_n(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows, int
 int chr_nf4_gemv_shape(int32_t n_rows, int32_t K_pad, int32_t swiglu, int32_t out[6]);
 
 /* Row-split linear of a tensor-parallel shard with the exchange fused in: ONE
- * launch per rank computes this rank's FP32 partial W_shard . x_shard, pushes its
- * rows into every peer's receive buffer over NVLink (plain peer stores), raises a
- * per-CTA flag on each peer, waits (bounded) for the peers' flags, sums the
- * partials in rank order, adds the residual and rounds once:
+ * launch per rank computes this rank's FP32 partial W_shard . x_shard, pushes every
+ * row into every peer's receive buffer over NVLink as one 8-byte word (value, call
+ * epoch) with plain peer stores, polls (bounded) its own buffer for the peers' words of
+ * the same rows, sums the partials in rank order, adds the residual and rounds once:
  *   y[m] = bf16( f32(y[m]) + sum_r partial_r[m] )      (y: bf16 [M], in place)
  * Every rank ends with the same y. The same CTA owns the same rows on every rank
- * (same matrix shape, same GPU model), so a CTA only waits for its namesakes.
+ * (same matrix shape, same GPU model). No fence and no separate flag is on the path:
+ * the word carries its own arrival mark.
  * Buffers (all device memory, mapped into every rank's address space, e.g.
  * symmetric memory or CUDA IPC; zeroed once before the first call):
- *   recv[p]  rank p's receive buffer: 2 * world * capacity floats (two epochs x
- *            one slot of `capacity` rows per source rank); M > capacity -> -7;
- *   flags[p] rank p's flag words: world * CHR_NF4_AR_MAX_CTAS uint32;
+ *   recv[p]  rank p's receive buffer: 2 * world * capacity 8-byte words (two halves
+ *            that calls alternate between x one slot of `capacity` rows per source
+ *            rank); M > capacity -> -7;
+ *   flags[p] rank p's flag words: world * CHR_NF4_AR_MAX_CTAS uint32 (used by
+ *            chr_nf4_pick_commit_tp, not by this entry);
  *   epoch    this rank's own uint32[2] {calls completed, exit ticket};
  *   status   this rank's own int32, set to 1 when a wait ran out of polls
- *            (2^22 unless chr_nf4_set_peer_polls changed it; the sum then
- *            includes whatever had arrived, and later calls stop waiting until
- *            the host clears the word).
+ *            (2^22 unless chr_nf4_set_peer_polls changed it; the sum then leaves
+ *            the missing partials out, and later calls stop waiting until the host
+ *            clears the word).
  * All ranks must issue the same sequence of calls on these buffers and tile the
  * rows alike: when the ranks' K shares differ, each passes the largest K_pad of
  * the layer in shape_k_pad. Capturable
@@ -291,7 +295,7 @@ int chr_nf4_pick_commit_tp(const void *logits_local, int32_t n_local, int32_t in
  * to the host's memory pool, code under a no-allocation rule). No counterpart in
  * the reference. The split partials go to a 1 MiB array built into the library
  * (resident on every GPU that loads it); the call returns -7 when
- * n_q * min(n_split, 16) * (hd + 2) exceeds 262144 floats. It calls no
+ * n_q * min(n_split, 32) * (hd + 2) exceeds 262144 floats. It calls no
  * allocation routine. The first call on a device looks the array's address up
  * (one host-side runtime query) and should therefore come before any stream
  * capture on that device; the device that owns `stream` must be the current one. All calls share the array: nothing in it has to start

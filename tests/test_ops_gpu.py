@@ -608,7 +608,8 @@ def test_peer_waits_run_out_and_report_instead_of_hanging():
     xt, xf = bf16_vec(rng, k)
 
     def peers_for(capacity):
-        bufs = [torch.zeros(2 * 2 * capacity + 2 * AR_MAX_CTAS, dtype=torch.float32, device="cuda")
+        n_recv = 2 * 2 * capacity * 2      # halves x ranks x rows, 8-byte words, in floats
+        bufs = [torch.zeros(n_recv + 2 * AR_MAX_CTAS, dtype=torch.float32, device="cuda")
                 for _ in range(2)]
         epoch = torch.zeros(2, dtype=torch.int32, device="cuda")
         status = torch.zeros((), dtype=torch.int32, device="cuda")
@@ -616,7 +617,7 @@ def test_peer_waits_run_out_and_report_instead_of_hanging():
         pr.rank, pr.world, pr.capacity = 0, 2, capacity
         for r, b in enumerate(bufs):
             pr.recv[r] = b.data_ptr()
-            pr.flags[r] = b.data_ptr() + 4 * 2 * 2 * capacity
+            pr.flags[r] = b.data_ptr() + 4 * n_recv
         pr.epoch, pr.status = epoch.data_ptr(), status.data_ptr()
         return pr, (bufs, epoch, status)
 
