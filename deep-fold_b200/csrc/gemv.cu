@@ -113,47 +113,47 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
   // peer is gone: do not spend the full poll budget again on every call
   const bool give_up = *reinterpret_cast<volatile int *>(pa.status) != 0;
 
-  // Rows of this CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of G*R rows.
+  // Rows of this CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of G*R rows. All of
+  // them are exchanged in one pass, a row per thread, so that the round trips overlap.
   const int rt = a.G * R;
+  const int my_tiles = blockIdx.x < a.n_tiles ? (a.n_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
   __nv_bfloat16 *y = a.y[0];
-  for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
-    for (int u = tid; u < rt; u += blockDim.x) {
-      const int row = tile * rt + u;
-      if (row >= M) continue;
-      const float own = __ldcg(mine + row);
-      // 1. push (value, epoch) into every peer's slot for this rank
-      for (int p = 0; p < pa.world; ++p) {
-        if (p != pa.rank) {
-          asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(slot_of(p, e, pa.rank) + row),
-                       "r"(__float_as_uint(own)), "r"(e)
-                       : "memory");
-        }
+  for (int idx = tid; idx < my_tiles * rt; idx += blockDim.x) {
+    const int row = (blockIdx.x + (idx / rt) * gridDim.x) * rt + idx % rt;
+    if (row >= M) continue;
+    const float own = __ldcg(mine + row);
+    // 1. push (value, epoch) into every peer's slot for this rank
+    for (int p = 0; p < pa.world; ++p) {
+      if (p != pa.rank) {
+        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(slot_of(p, e, pa.rank) + row),
+                     "r"(__float_as_uint(own)), "r"(e)
+                     : "memory");
       }
-      // 2. collect the peers' words for the same row, summing in rank order
-      float v = 0.f;
-      for (int r = 0; r < pa.world; ++r) {
-        if (r == pa.rank) {
-          v += own;
-          continue;
-        }
-        const uint2 *src = slot_of(pa.rank, e, r) + row;
-        uint32_t bits = 0u, seen = 0u;
-        unsigned int polls = 0;
-        for (;;) {
-          asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(seen) : "l"(src)
-                       : "memory");
-          if (seen == e || give_up) break;
-          if (++polls >= pa.polls) {
-            atomicExch(pa.status, 1);
-            break;
-          }
-        }
-        v += seen == e ? __uint_as_float(bits) : 0.f;
-      }
-      // 3. add the residual, round once
-      v += __bfloat162float(y[row]);
-      y[row] = __float2bfloat16(v);
     }
+    // 2. collect the peers' words for the same row, summing in rank order
+    float v = 0.f;
+    for (int r = 0; r < pa.world; ++r) {
+      if (r == pa.rank) {
+        v += own;
+        continue;
+      }
+      const uint2 *src = slot_of(pa.rank, e, r) + row;
+      uint32_t bits = 0u, seen = 0u;
+      unsigned int polls = 0;
+      for (;;) {
+        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(seen) : "l"(src)
+                     : "memory");
+        if (seen == e || give_up) break;
+        if (++polls >= pa.polls) {
+          atomicExch(pa.status, 1);
+          break;
+        }
+      }
+      v += seen == e ? __uint_as_float(bits) : 0.f;
+    }
+    // 3. add the residual, round once
+    v += __bfloat162float(y[row]);
+    y[row] = __float2bfloat16(v);
   }
   // 4. the last CTA out publishes the new epoch
   __syncthreads();
