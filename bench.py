@@ -291,10 +291,16 @@ def run_ours(args, spec) -> None:
         weights = shard_weights(weights, rank, world)
         torch.cuda.empty_cache()
     spec = weights.spec
-    if args.batch != 1:
+    if args.batches != [1]:
         if world > 1:
             raise SystemExit("--batch > 1 runs on one GPU")
-        return run_batched(args, spec, weights, local)
+        for b in args.batches:
+            args.batch = b
+            run_batched(args, spec, weights, local)
+            torch.cuda.empty_cache()
+        return
+    if args.prefill_sweep:
+        return run_prefill_sweep(args, spec, full_spec, weights, comm, rank, world)
     loop = DecodeV2Loop.from_weights(weights, comm=comm)
     exchange = "none"
     if comm is not None:
@@ -473,6 +479,29 @@ def run_ours(args, spec) -> None:
         breakdown["unit"] = "us per launch (layers_ms: all layers, ms)"
         check_status("after the breakdown sweeps")
 
+    # cost of the exchange fused into the row-split linears: the fused launch minus the
+    # partial-only launch of the same shard, swept over all layers (collective: every
+    # rank runs both sweeps)
+    exchange_us = None
+    if spec.tp > 1 and state.peers is not None:
+        from gpu.decodev2 import step as stepmod
+        from gpu.nf4 import nf4_gemv_f32
+
+        def sweep_of(fn):
+            def run():
+                for ly in layers:
+                    fn(ly)
+            return graph_timed(run, 3, torch) * 1e3 / len(layers)
+
+        exchange_us = {}
+        for name, pick, src in (("o_proj", lambda ly: ly.o, ar.attn), ("down_proj", lambda ly: ly.down, ar.down_in)):
+            fused = sweep_of(lambda ly: stepmod._accumulate(state, pick(ly), src, ar.x))
+            alone = sweep_of(lambda ly: nf4_gemv_f32(pick(ly).packed, pick(ly).scale, src.reshape(pick(ly).K),
+                                                    pick(ly).M, pick(ly).K, pick(ly).K_pad, ar.partial,
+                                                    pick(ly).bias))
+            exchange_us[name] = {"fused": fused, "partial_only": alone, "exchange": fused - alone}
+        check_status("after the exchange sweeps")
+
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local}")
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -516,12 +545,59 @@ def run_ours(args, spec) -> None:
         line["step_breakdown"] = breakdown
     line["step_mode"] = "launch chain in one CUDA graph"
     line["row_split_exchange"] = exchange
+    if exchange_us is not None:
+        line["exchange_us"] = exchange_us
     line["prefill_mode"] = prefill_mode
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(full_spec)
     print(json.dumps(line), flush=True)
     if comm is not None:
         del step
+        comm.shutdown(loop)
+
+
+def run_prefill_sweep(args, spec, full_spec, weights, comm, rank: int, world: int) -> None:
+    """``--prefill-sweep``: chunked prefill of prompts of the given lengths on one set of
+    weights; device time per length (max over ranks), one JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    from gpu.decodev2 import DecodeV2Loop
+    from gpu.nf4 import _lib
+
+    loop = DecodeV2Loop.from_weights(weights, comm=comm)
+    gen = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, spec.vocab, (max(args.sweep),), generator=gen).tolist()
+    loop.reset()
+    loop.prefill_from(ids[: min(args.sweep)], 0, chunk=args.chunk)      # lazy kernel loads
+    rows = []
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    for n in args.sweep:
+        best = None
+        for _ in range(2 if n >= 1024 else 3):
+            loop.reset()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ev[0].record()
+            loop.prefill_from(ids[:n], 0, chunk=args.chunk)
+            ev[1].record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([ev[0].elapsed_time(ev[1])], dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            best = float(ms) if best is None else min(best, float(ms))
+        rows.append({"tokens": n, "ms": best, "tok_s": n / (best / 1e3),
+                     "tflops": 2.0 * full_spec.packed_bytes_per_token() / 0.53125 * n / (best / 1e3) / 1e12})
+    if _lib.load().chr_nf4_gemv_status() != 0:
+        raise SystemExit("GEMV status word set")
+    if rank == 0:
+        print(json.dumps({"metric": "prefill_tok_s", "unit": "tok/s", "n_gpus": world,
+                          "config": {"workload": f"{full_spec.name} chunked prefill sweep", "chunk": args.chunk,
+                                     "parallelism": f"tp{world}", "timing": "best of 2-3, device events, "
+                                     "max over ranks"},
+                          "prefill_sweep": rows}), flush=True)
+    if comm is not None:
         comm.shutdown(loop)
 
 
@@ -538,7 +614,9 @@ def run_batched(args, spec, weights, local: int) -> None:
     prompts = [torch.randint(0, spec.vocab, (args.prompt,),
                              generator=torch.Generator().manual_seed(2 + i)).tolist() for i in range(b)]
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    st.prefill(weights, prompts[:1] * b, chunk=args.chunk)        # untimed pass (lazy kernel loads)
+    if not getattr(args, "prefill_warm", False):
+        st.prefill(weights, prompts[:1] * b, chunk=args.chunk)    # untimed pass (lazy kernel loads)
+        args.prefill_warm = True
     torch.cuda.synchronize()
     ev[0].record()
     st.prefill(weights, prompts, chunk=args.chunk)
@@ -617,7 +695,12 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=None,
                     help="prompt tokens (default: fills the context up to the timed steps)")
     ap.add_argument("--chunk", type=int, default=512, help="prefill chunk width")
-    ap.add_argument("--batch", type=int, default=1, help="sequences decoded together")
+    ap.add_argument("--batch", default="1",
+                    help="sequences decoded together; a comma list runs one line per size on one "
+                         "set of weights")
+    ap.add_argument("--prefill-sweep", default="",
+                    help="comma list of prompt lengths: time the chunked prefill of each and print "
+                         "one JSON line with the table (no decode window)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--breakdown", action="store_true",
                     help="also time every operation kind of the step on its own (per-layer sweeps)")
@@ -628,9 +711,14 @@ def main() -> None:
                          "inside the GEMV launch over peer memory")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
-    from gpu.decodev2.arch import CONFIGS
+    args.batches = [int(b) for b in str(args.batch).split(",")]
+    args.batch = args.batches[0]
+    from gpu.decodev2.arch import CONFIGS, with_max_seq
 
     spec = CONFIGS[args.model]
+    if args.prefill_sweep:
+        args.sweep = [int(n) for n in args.prefill_sweep.split(",")]
+        spec = with_max_seq(spec, max(spec.max_seq, max(args.sweep) + 64))
     if args.prompt is None:
         # leave room for the first ids, the warm-up and two timed windows
         room = 16 + 2 * (args.warmup + args.steps) + 8

@@ -23,7 +23,7 @@ OUT_DIR = CSRC.parent / "gpu" / "nf4"
 LIB = OUT_DIR / "libchr_nf4.so"
 OBJ_DIR = CSRC / "build"
 
-CUDA_SOURCES = ("gemv.cu", "decode_ops.cu", "prefill_ops.cu", "gemm.cu", "gemm_tc.cu", "codec_dev.cu",
+CUDA_SOURCES = ("gemv.cu", "decode_ops.cu", "prefill_ops.cu", "prefill_attn.cu", "gemm.cu", "gemm_tc.cu", "codec_dev.cu",
                 "version.cu")
 CXX_SOURCES = ("codec.cpp",)
 HEADERS = ("nf4_common.cuh", "gemv_ring.cuh", "gemv_n.cuh", "attn_core.cuh", "gemm_plan.h")

@@ -477,7 +477,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(in_full(s), 1);
-      mbar_init(ab_full(s), rDequant);
+      mbar_init(ab_full(s), tBM * MT);
       mbar_init(empty(s), 1);
     }
     mbar_init(acc_full, 1);
@@ -542,15 +542,19 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
       }
     }
   } else {
-    // -------- dequant: thread (row r, part) owns 64 / rParts codes of the K tile --------
+    // -------- dequant: one thread per (weight row, K tile) --------
+    // A K tile is one NF4 group, so a row has ONE scale per tile: the thread rounds the
+    // 16 products LUT[i] * scale to bf16 once (the reference's A operand, bit for bit:
+    // gpu/nf4/nf4_gemm.cu:319-323 rounds LUT[code] * scale per weight, which is the same
+    // 16 values), keeps them in registers as a low-byte and a high-byte plane, and turns
+    // the tile's 64 codes into bf16 with byte permutes: no shared-memory lookup and no
+    // multiply per weight. The thread groups take the K tiles in turn.
     constexpr int kRows = tBM * MT;
-    constexpr int rParts = rDequant / kRows;  // threads per weight row
-    static_assert(rParts == 1 || rParts == 2 || rParts == 4, "threads per row");
-    constexpr int kBytes = 32 / rParts;     // packed bytes per thread per K tile
-    constexpr int kChunks = kBytes / 4;     // 8-code chunks (16 bytes of bf16 out)
+    constexpr int kTeams = rDequant / kRows;  // thread groups, one K tile each at a time
+    static_assert(kTeams >= 1 && rDequant % kRows == 0, "dequant threads per row tile");
     const int t = tid - 64;
     const int r = t % kRows;                // row inside the CTA's MT tiles
-    const int part = t / kRows;
+    const int team = t / kRows;
     const int grow = m0 + r;
     const bool row_live = grow < M;
     const int n_groups = K_pad / kGroup;
@@ -560,52 +564,62 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
     const int sw = rr & 7;
     bool ok = true;
     uint16_t s_bits = 0;
-    if (row_live && n_local > 0) s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt0);
-    for (int i = 0; i < n_local && ok; ++i) {
+    if (row_live && team < n_local) {
+      s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt0 + team);
+    }
+    for (int i = team; i < n_local && ok; i += kTeams) {
       const int s = i % kStages;
       const int kt = kt0 + i;
       const float sc = row_live ? half_bits_to_float(s_bits) : 0.f;
-      if (row_live && i + 1 < n_local) {
-        s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt + 1);
+      if (row_live && i + kTeams < n_local) {
+        s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt + kTeams);
+      }
+      // the 16 values of this (row, group), two bf16 per word, then as byte planes
+      uint32_t lo_plane[4], hi_plane[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t p0 = pack_bf16(lut[4 * j] * sc, lut[4 * j + 1] * sc);
+        const uint32_t p1 = pack_bf16(lut[4 * j + 2] * sc, lut[4 * j + 3] * sc);
+        lo_plane[j] = __byte_perm(p0, p1, 0x6420);
+        hi_plane[j] = __byte_perm(p0, p1, 0x7531);
       }
       if (i >= kStages) ok = mbar_wait(empty(s), ((i / kStages) - 1) & 1);
       if (!ok) break;
       ok = mbar_wait(in_full(s), (i / kStages) & 1);
       if (!ok) break;
-      uint32_t wv[kChunks];
-      if constexpr (kChunks == 8) {
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(wv[0]), "=r"(wv[1]), "=r"(wv[2]), "=r"(wv[3])
-                     : "r"(raw_tile(s) + r * 32));
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(wv[4]), "=r"(wv[5]), "=r"(wv[6]), "=r"(wv[7])
-                     : "r"(raw_tile(s) + r * 32 + 16));
-      } else if constexpr (kChunks == 4) {
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(wv[0]), "=r"(wv[1]), "=r"(wv[2]), "=r"(wv[3])
-                     : "r"(raw_tile(s) + r * 32 + part * kBytes));
-      } else {
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];"
-                     : "=r"(wv[0]), "=r"(wv[1])
-                     : "r"(raw_tile(s) + r * 32 + part * kBytes));
-      }
-      const int k_base = kt * tBK + part * (64 / rParts);
-      const bool whole = k_base + 64 / rParts <= K;  // no K tail inside this thread's codes
+      uint32_t wv[8];
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(wv[0]), "=r"(wv[1]), "=r"(wv[2]), "=r"(wv[3])
+                   : "r"(raw_tile(s) + r * 32));
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(wv[4]), "=r"(wv[5]), "=r"(wv[6]), "=r"(wv[7])
+                   : "r"(raw_tile(s) + r * 32 + 16));
+      const int k_base = kt * tBK;
+      const bool whole = k_base + tBK <= K;  // no K tail inside this tile
 #pragma unroll
-      for (int c4 = 0; c4 < kChunks; ++c4) {
-        const int c = part * kChunks + c4;
+      for (int c = 0; c < 8; ++c) {
         uint32_t o[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t byte = (wv[c4] >> (8 * e)) & 0xFFu;
-          float lo = lut[byte & 0xFu] * sc;
-          float hi = lut[byte >> 4] * sc;
-          if (!whole) {
-            const int k = k_base + c4 * 8 + 2 * e;
-            if (k >= K) lo = 0.f;
-            if (k + 1 >= K) hi = 0.f;
+        for (int h = 0; h < 2; ++h) {
+          // four codes (nibbles, k order) -> four bf16: entry = table[code & 7] from the
+          // lower or the upper half of the table, chosen per byte by the code's bit 3
+          const uint32_t codes = h == 0 ? (wv[c] & 0xFFFFu) : (wv[c] >> 16);
+          const uint32_t sel = codes & 0x7777u;
+          const uint32_t pick = ((codes & 0x8888u) >> 1) + 0x3210u;
+          const uint32_t lo = __byte_perm(__byte_perm(lo_plane[0], lo_plane[1], sel),
+                                          __byte_perm(lo_plane[2], lo_plane[3], sel), pick);
+          const uint32_t hi = __byte_perm(__byte_perm(hi_plane[0], hi_plane[1], sel),
+                                          __byte_perm(hi_plane[2], hi_plane[3], sel), pick);
+          o[2 * h] = __byte_perm(lo, hi, 0x5140);
+          o[2 * h + 1] = __byte_perm(lo, hi, 0x7362);
+        }
+        if (!whole) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int k = k_base + c * 8 + 2 * e;
+            if (k >= K) o[e] &= 0xFFFF0000u;
+            if (k + 1 >= K) o[e] &= 0x0000FFFFu;
           }
-          o[e] = pack_bf16(lo, hi);
         }
         const uint32_t dst = a_tile(s) + a_row_off + static_cast<uint32_t>((c ^ sw) * 16);
         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o[0]), "r"(o[1]),

@@ -1,8 +1,10 @@
 """Chunked prompt prefill: tensor-core NF4 GEMM for the linears, eager (not captured).
 
-Follows the reference (gpu/decodev2/prefill.py:26-141): chunks of at most
-``LIVE_MAX_N`` positions, RMSNorm / RoPE / causal GQA attention as torch ops in
-the cache dtype, KV rows written by slice, lm_head only on the last chunk.
+Follows the reference (gpu/decodev2/prefill.py:26-141): chunks of positions, RMSNorm /
+RoPE / causal GQA attention in the cache dtype, KV rows written per chunk, lm_head only
+on the last chunk. The attention of a chunk over the cache prefix is this library's
+``chr_nf4_attn_prefill`` kernel (the reference calls torch's
+``scaled_dot_product_attention`` with a boolean mask there, prefill.py:50-92).
 """
 
 from __future__ import annotations
@@ -10,7 +12,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from gpu.nf4 import LIVE_MAX_N, nf4_rms_rows, nf4_rope_kv_rows, nf4_silu_mul
+from gpu.nf4 import LIVE_MAX_N, nf4_attn_prefill, nf4_rms_rows, nf4_rope_kv_rows, nf4_silu_mul
 
 from .arch import ArchSpec
 from .embed import gather_embed
@@ -64,14 +66,17 @@ def _split_qkv(layer: DeviceLayer, h: torch.Tensor, spec: ArchSpec):
     )
 
 
-def _attend(q, k, v, spec: ArchSpec, mask) -> torch.Tensor:
-    """``q`` [n, n_q, hd]; ``k``/``v`` [1, n_kv, seq, hd]; bool mask [1, 1, n, seq]."""
-    n = int(q.shape[0])
-    a = F.scaled_dot_product_attention(
-        q.permute(1, 0, 2).unsqueeze(0), k, v, attn_mask=mask, scale=spec.attn_scale,
-        enable_gqa=spec.n_q != spec.n_kv,
-    )
-    return a.squeeze(0).permute(1, 0, 2).reshape(n, spec.q_dim)
+ATTN_HEAD_DIMS = (16, 32, 64, 128)
+
+
+def _attend(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, spec: ArchSpec,
+            start: int) -> torch.Tensor:
+    """``q`` [n, n_q, hd] (rotated) against cache rows ``0 .. start+n-1`` of one layer
+    (``[max_seq, n_kv, hd]``, the chunk's rows already written) -> ``[n, q_dim]``."""
+    if q.dtype is not torch.bfloat16 or spec.head_dim not in ATTN_HEAD_DIMS:
+        raise RuntimeError(f"prefill attention covers bfloat16 caches with head_dim in {ATTN_HEAD_DIMS}; "
+                           f"got {q.dtype}, head_dim={spec.head_dim}")
+    return nf4_attn_prefill(q, k_cache, v_cache, start, spec.attn_scale)
 
 
 def _reduced(state: DecodeState, partial: torch.Tensor) -> torch.Tensor:
@@ -98,8 +103,6 @@ def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch
     dtype = state.arena.x.dtype
     x = gather_embed(weights.embed, ids, dtype=dtype)
     cos, sin = state.cos[start:seq], state.sin[start:seq]
-    q_pos = torch.arange(start, seq, device=state.device).unsqueeze(1)
-    mask = (torch.arange(seq, device=state.device).unsqueeze(0) <= q_pos)[None, None]
     fused = _FUSED_ROWS and x.dtype is torch.bfloat16 and spec.hidden % 8 == 0
     for li, layer in enumerate(weights.layers):
         if fused:
@@ -115,8 +118,8 @@ def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch
             q = apply_rope_torch(q, cos, sin)
             k = apply_rope_torch(k, cos, sin)
             state.kv.write_range(li, start, k, v)
-        k_all, v_all = state.kv.view(li, seq)
-        x = x + _reduced(state, nf4_linear(layer.o, _attend(q, k_all, v_all, spec, mask)))
+        attn = _attend(q.contiguous(), state.kv.k[li], state.kv.v[li], spec, start)
+        x = x + _reduced(state, nf4_linear(layer.o, attn))
         if fused:
             h = nf4_rms_rows(x, layer.norm2, spec.rms_eps)
         else:

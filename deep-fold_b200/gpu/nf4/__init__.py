@@ -44,6 +44,7 @@ __all__ = [
     "nf4_rms_rows",
     "nf4_rope_kv_rows",
     "nf4_silu_mul",
+    "nf4_attn_prefill",
     "nf4_rope_kv",
     "nf4_set_pdl",
     "nf4_set_tuning",
@@ -798,6 +799,39 @@ def nf4_rope_kv_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache:
         _ptr(sin), int(start), n, int(n_q), int(n_kv), int(hd), max_seq, _stream())
     _lib.check(rc, "chr_nf4_rope_kv_rows")
     return q_out
+
+
+def nf4_attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, start: int,
+                     scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal GQA attention of a prefill chunk: query row ``i`` (position ``start + i``) over cache
+    rows ``t <= start + i``; ``q`` ``[n, n_q, hd]`` (or ``[n, n_q*hd]`` rows with a stride), caches
+    ``[max_seq, n_kv, hd]`` -> ``[n, n_q*hd]``. See ``chr_nf4_attn_prefill``."""
+    for t, what in ((k_cache, "k_cache"), (v_cache, "v_cache")):
+        if not t.is_cuda or t.dtype is not torch.bfloat16 or not t.is_contiguous() or t.dim() != 3:
+            _fail(f"{what} must be contiguous CUDA bfloat16 [max_seq, n_kv, hd]")
+    max_seq, n_kv, hd = (int(v) for v in k_cache.shape)
+    if tuple(v_cache.shape) != (max_seq, n_kv, hd):
+        _fail("k_cache and v_cache differ in shape")
+    if q.dim() == 3:
+        if q.stride(2) != 1 or q.stride(1) != q.size(2) or q.size(2) != hd:
+            _fail("q must be [n, n_q, hd] with contiguous heads")
+        q2 = q.as_strided((q.size(0), q.size(1) * q.size(2)), (q.stride(0), 1))
+    else:
+        q2 = q
+    n, qs = _rows_view(q2, "q")
+    width = int(q2.size(1))
+    if width % hd != 0 or (width // hd) % n_kv != 0:
+        _fail("q width must be n_q * hd with n_q a multiple of n_kv")
+    n_q = width // hd
+    if out is None:
+        out = torch.empty((n, width), dtype=torch.bfloat16, device=q.device)
+    elif (not out.is_cuda or out.dtype is not torch.bfloat16 or not out.is_contiguous()
+          or out.numel() != n * width):
+        _fail("out must be contiguous CUDA bfloat16 [n, n_q*hd]")
+    rc = _lib.load().chr_nf4_attn_prefill(_ptr(q2), qs, _ptr(k_cache), _ptr(v_cache), _ptr(out), n,
+                                          int(start), n_q, n_kv, hd, max_seq, float(scale), _stream())
+    _lib.check(rc, "chr_nf4_attn_prefill")
+    return out
 
 
 def nf4_silu_mul(gate_up: torch.Tensor, inter: int) -> torch.Tensor:

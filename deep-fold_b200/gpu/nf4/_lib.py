@@ -139,6 +139,11 @@ SIGNATURES = {
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p],
     ),
+    "chr_nf4_attn_prefill": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32,
+         c_int32, c_float, c_void_p],
+    ),
     "chr_nf4_silu_mul": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "chr_nf4_encode_f32": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int32]),
     "chr_nf4_decode_f32": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_int32]),

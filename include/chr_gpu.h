@@ -335,6 +335,23 @@ int chr_nf4_encode_dev(const float *w, int32_t M, int32_t K, uint8_t *packed,
 int chr_nf4_rms_rows(const void *x, int64_t x_stride, const void *w, void *y, int32_t N,
                      int32_t K, float eps, void *stream);
 
+/* Causal GQA attention of one prefill chunk (additive entry; the reference runs
+ * torch's scaled_dot_product_attention with a boolean mask per chunk,
+ * gpu/decodev2/prefill.py:50-92). Query row i (0 <= i < n, position start + i) attends
+ * cache rows t <= start + i:
+ *   out[i, h, :] = softmax_t( scale * q[i, h, :] . k_cache[t, h / n_rep, :] ) . v_cache[t, ...]
+ * q: bf16 [n, n_q, hd], rows q_stride elements apart (even, >= n_q*hd), already
+ * rotated; k_cache, v_cache: bf16 [max_seq, n_kv, hd] holding rows 0 .. start+n-1
+ * (the chunk's own rows included); out: bf16 [n, n_q*hd] contiguous. FP32 scores,
+ * running softmax and accumulation; the probabilities are rounded to bf16 for the
+ * value product. hd in {16, 32, 64, 128}; start + n <= max_seq. No mask tensor, no
+ * workspace. Capturable. Returns 0 or a negative code (-1 null, -3 dims,
+ * -5 alignment: caches 16 bytes, q / out 4 bytes, -6 launch). */
+int chr_nf4_attn_prefill(const void *q, int64_t q_stride, const void *k_cache,
+                         const void *v_cache, void *out, int32_t n, int32_t start,
+                         int32_t n_q, int32_t n_kv, int32_t hd, int32_t max_seq, float scale,
+                         void *stream);
+
 /* RoPE for N consecutive positions start..start+N-1 and the cache write of the
  * chunk: q [N, n_q, hd] (rows q_stride apart) is rotated into q_out (contiguous),
  * k is rotated into k_cache rows, v copied into v_cache rows (caches bf16

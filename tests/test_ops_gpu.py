@@ -523,6 +523,64 @@ def test_prefill_row_kernels_match_the_torch_ops_bit_for_bit():
     assert (y.float() - ref).abs().max() <= 2 ** -7 * ref.abs().max()
 
 
+PREFILL_ATTN_CASES = [
+    # n, start, n_q, n_kv, hd, max_seq
+    (37, 11, 8, 2, 64, 96),        # ragged chunk in the middle of the cache
+    (1, 0, 4, 4, 16, 8),           # one query, one key, no grouping
+    (64, 0, 5, 1, 128, 64),        # exactly one tile, five heads on one kv head
+    (130, 200, 10, 2, 128, 512),   # several key tiles before the diagonal one
+    (512, 512, 10, 2, 128, 1024),  # the benchmark's chunk width against a 512-row prefix
+    (33, 95, 6, 3, 32, 128),       # the chunk ends on the last cache row
+]
+
+
+@pytest.mark.parametrize("n,start,n_q,n_kv,hd,max_seq", PREFILL_ATTN_CASES)
+def test_prefill_attention_matches_masked_softmax_in_f32(n, start, n_q, n_kv, hd, max_seq):
+    """``chr_nf4_attn_prefill`` against softmax(scale * q k^T + causal mask) v evaluated in
+    float32 on the same bf16 inputs (the reference's per-chunk attention,
+    gpu/decodev2/prefill.py:50-92). Tolerance: 0.02 of the largest output, the bound the
+    model oracle puts on attention."""
+    from gpu.nf4 import nf4_attn_prefill
+
+    gen = torch.Generator(device="cuda").manual_seed(n * 131 + start)
+    wide = torch.randn((n, n_q * hd + 16), generator=gen, device="cuda").to(torch.bfloat16)
+    q = wide[:, : n_q * hd]                     # rows with a stride, as a slice of a GEMM output
+    k_cache = torch.randn((max_seq, n_kv, hd), generator=gen, device="cuda").to(torch.bfloat16)
+    v_cache = torch.randn((max_seq, n_kv, hd), generator=gen, device="cuda").to(torch.bfloat16)
+    # rows past the prefix must not matter, whatever they hold
+    k_cache[start + n:] = float("nan")
+    v_cache[start + n:] = float("nan")
+    scale = hd ** -0.5
+    got = nf4_attn_prefill(q, k_cache, v_cache, start, scale).float().reshape(n, n_q, hd)
+
+    seq = start + n
+    qf = q.float().reshape(n, n_q, hd)
+    kf = k_cache[:seq].float().repeat_interleave(n_q // n_kv, dim=1)
+    vf = v_cache[:seq].float().repeat_interleave(n_q // n_kv, dim=1)
+    scores = torch.einsum("ihd,thd->hit", qf, kf) * scale
+    allowed = torch.arange(seq, device="cuda")[None, :] <= (start + torch.arange(n, device="cuda"))[:, None]
+    scores = scores.masked_fill(~allowed[None], float("-inf"))
+    want = torch.einsum("hit,thd->ihd", torch.softmax(scores, dim=-1), vf)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() <= 0.02 * want.abs().max()
+    # 3-D query tensors take the same path
+    again = nf4_attn_prefill(q.reshape(n, n_q, hd).contiguous(), k_cache, v_cache, start, scale)
+    assert torch.equal(again.float().reshape(n, n_q, hd), got)
+
+
+def test_prefill_attention_rejects_what_it_does_not_cover():
+    from gpu.nf4 import nf4_attn_prefill
+
+    k = torch.zeros((32, 2, 48), dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros((4, 4 * 48), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        nf4_attn_prefill(q, k, k, 0, 0.1)                      # head_dim 48
+    k = torch.zeros((32, 2, 64), dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros((4, 4 * 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        nf4_attn_prefill(q, k, k, 30, 0.1)                     # 30 + 4 rows in a 32-row cache
+
+
 GEMV_N_CASES = [
     (2048, 2048, 2), (2560, 5120, 3), (1024, 5120, 8), (520, 13824, 4), (300, 27648, 8),
     (6144, 6144, 4), (130, 65, 3), (333, 1000, 8), (64, 16384, 5), (7, 64, 1),
