@@ -41,8 +41,10 @@ UNIT = "tok/s"
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of one launch
-# of the timed SwiGLU GEMV, from the ncu capture summarised under profiles/.
-NCU_TRAFFIC_RATIO = 1.001
+# of the timed SwiGLU GEMV, from the ncu capture of the 32B gate/up launch summarised in
+# profiles/nf4_gemv_swiglu_32b_gate_up.md (150.46 MB read + 3.7-4.4 MB written for
+# 150.47 MB): other models' launches are scaled by their algorithmic bytes.
+NCU_TRAFFIC_RATIO = 1.027
 
 
 def measured_peaks() -> dict:
@@ -537,8 +539,8 @@ def run_ours(args, spec) -> None:
                         "frac_of_nominal_8tbs": achieved / 8000.0,
                         "bytes_per_launch": per_launch, "us_per_launch": k_us,
                         "traffic": int(round(per_launch * NCU_TRAFFIC_RATIO)),
-                        "traffic_source": "ncu capture of one gate/up launch (profiles/), scaled by "
-                                          "algorithmic bytes"}
+                        "traffic_source": "ncu capture of one 32B gate/up launch "
+                                          "(profiles/nf4_gemv_swiglu_32b_gate_up.md), scaled by algorithmic bytes"}
     if gemm_roof is not None:
         line["gemm_roofline"] = gemm_roof
     if breakdown is not None:

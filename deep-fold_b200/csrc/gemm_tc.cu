@@ -563,16 +563,20 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
                                                      (rr & 7) * 128);
     const int sw = rr & 7;
     bool ok = true;
-    uint16_t s_bits = 0;
-    if (row_live && team < n_local) {
-      s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt0 + team);
-    }
+    // scales of this thread's next two K tiles are kept in flight
+    const uint16_t *srow = scale + static_cast<size_t>(row_live ? grow : 0) * n_groups + kt0;
+    uint16_t s_now = 0, s_next = 0;
+    if (row_live && team < n_local) s_now = __ldg(srow + team);
+    if (row_live && team + kTeams < n_local) s_next = __ldg(srow + team + kTeams);
     for (int i = team; i < n_local && ok; i += kTeams) {
       const int s = i % kStages;
       const int kt = kt0 + i;
-      const float sc = row_live ? half_bits_to_float(s_bits) : 0.f;
-      if (row_live && i + kTeams < n_local) {
-        s_bits = __ldg(scale + static_cast<size_t>(grow) * n_groups + kt + kTeams);
+      const float sc = row_live ? half_bits_to_float(s_now) : 0.f;
+      s_now = s_next;
+      if (row_live && i + 2 * kTeams < n_local) s_next = __ldg(srow + i + 2 * kTeams);
+      // 16 scales share a 32-byte sector: ask for the row's next sector well ahead
+      if (row_live && i + 24 < n_local) {
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(srow + i + 24));
       }
       // the 16 values of this (row, group), two bf16 per word, then as byte planes
       uint32_t lo_plane[4], hi_plane[4];
@@ -599,13 +603,15 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t o[4];
+        // eight codes (nibbles, k order) -> eight bf16: entry = table[code & 7] from the
+        // lower or the upper half of the table, chosen per byte by the code's bit 3. A
+        // permute reads the low 16 bits of its selector: four codes per permute.
+        const uint32_t sel8 = wv[c] & 0x77777777u;
+        const uint32_t pick8 = ((wv[c] & 0x88888888u) >> 1) + 0x32103210u;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          // four codes (nibbles, k order) -> four bf16: entry = table[code & 7] from the
-          // lower or the upper half of the table, chosen per byte by the code's bit 3
-          const uint32_t codes = h == 0 ? (wv[c] & 0xFFFFu) : (wv[c] >> 16);
-          const uint32_t sel = codes & 0x7777u;
-          const uint32_t pick = ((codes & 0x8888u) >> 1) + 0x3210u;
+          const uint32_t sel = h == 0 ? sel8 : sel8 >> 16;
+          const uint32_t pick = h == 0 ? pick8 : pick8 >> 16;
           const uint32_t lo = __byte_perm(__byte_perm(lo_plane[0], lo_plane[1], sel),
                                           __byte_perm(lo_plane[2], lo_plane[3], sel), pick);
           const uint32_t hi = __byte_perm(__byte_perm(hi_plane[0], hi_plane[1], sel),

@@ -26,7 +26,26 @@ __global__ void __launch_bounds__(256) rms_rows_kernel(const __nv_bfloat16 *__re
   const __nv_bfloat16 *xr = x + static_cast<size_t>(row) * x_stride;
   const float s = rsqrtf(warp_sumsq_bf16(xr, K, lane) / static_cast<float>(K) + eps);
   __nv_bfloat16 *yr = y + static_cast<size_t>(row) * K;
-  for (int i = lane; i < K; i += 32) {
+  // 8 elements per lane and step where the row, the weight and the output allow
+  // 16-byte accesses; the same products, rounded the same way, as the scalar tail
+  const bool wide = ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(w) |
+                      reinterpret_cast<uintptr_t>(yr)) & 15) == 0;
+  const int k8 = wide ? (K & ~7) : 0;
+  for (int i = lane * 8; i < k8; i += 256) {
+    const uint4 xv = *reinterpret_cast<const uint4 *>(xr + i);
+    const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(w + i));
+    const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
+    const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 r = __floats2bfloat162_rn(bf16_lo(ws[e]) * bf16_lo(xs[e]) * s,
+                                                     bf16_hi(ws[e]) * bf16_hi(xs[e]) * s);
+      o[e] = *reinterpret_cast<const uint32_t *>(&r);
+    }
+    *reinterpret_cast<uint4 *>(yr + i) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  for (int i = k8 + lane; i < K; i += 32) {
     yr[i] = __float2bfloat16(__bfloat162float(w[i]) * __bfloat162float(xr[i]) * s);
   }
 }
