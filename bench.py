@@ -668,7 +668,7 @@ def run_batched(args, spec, weights, local: int) -> None:
     peaks = measured_peaks()
     step_bytes = spec.packed_bytes_per_token()
     tokens = args.steps * b
-    path = "chr_nf4_gemv_n (CUDA cores, FP32 weights)" if b <= 8 else "chr_nf4_gemm_rows (tcgen05)"
+    path = "chr_nf4_gemv_n (CUDA cores, FP32 weights)" if b <= 4 else "chr_nf4_gemm_rows (tcgen05)"
     line = {
         "metric": f"decode_tok_s_bs{b}", "value": tokens / (dev_ms / 1e3), "unit": UNIT, "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,

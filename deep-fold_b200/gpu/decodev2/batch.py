@@ -10,10 +10,11 @@ per layer [RMSNorm rows, q/k/v linear, attention of B sequences in one launch,
 o-proj + residual, RMSNorm rows, gate/up linear, SiLU*up, down-proj + residual]
 -> final RMSNorm -> lm_head -> one greedy pick + commit per sequence.
 
-Linears: up to 8 sequences run through the CUDA-core N-column GEMV
-(``chr_nf4_gemv_n``: FP32 weights, the numerics of the one-sequence step); larger
-batches through the tensor-core GEMM on activation rows (bf16 weight operand, as in
-prefill). Single GPU only.
+Linears: up to ``GEMV_ROWS`` (4) sequences run through the CUDA-core multi-row GEMV
+(``chr_nf4_gemv_n``: FP32 weights, the numerics of the one-sequence step; one launch
+carries four rows for the price of one pass over the weights); larger batches through
+the tensor-core GEMM on activation rows (bf16 weight operand, as in prefill), whose
+pass over the weights costs less than two GEMV launches. Single GPU only.
 """
 
 from __future__ import annotations
@@ -31,7 +32,10 @@ from .linear import DeviceLinear, DeviceWeights
 from .runner import consume_prompt
 from .state import DecodeState, GraphSafeKV
 
-__all__ = ["BatchState", "BatchLoop", "batched_greedy_decode"]
+__all__ = ["BatchState", "BatchLoop", "batched_greedy_decode", "GEMV_ROWS"]
+
+#: sequences up to which the linears take the CUDA-core GEMV (one launch of four rows)
+GEMV_ROWS = min(4, GEMV_MAX_N)
 
 
 class BatchState:
@@ -107,7 +111,7 @@ def _linear(mat: DeviceLinear, rows: torch.Tensor, out: torch.Tensor | None = No
             add: torch.Tensor | None = None) -> torch.Tensor:
     """``rows [B, K] @ W.T (+ bias) (+ add)`` -> ``[B, M]``."""
     n = int(rows.size(0))
-    if n <= GEMV_MAX_N:
+    if n <= GEMV_ROWS:
         return nf4_gemv_n(mat.packed, mat.scale, rows, mat.M, mat.K, mat.K_pad, out=out, add=add,
                           bias=mat.bias)
     y = nf4_gemm_rows(mat.packed, mat.scale, rows, mat.M, mat.K, mat.K_pad)

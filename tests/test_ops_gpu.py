@@ -645,7 +645,9 @@ def test_gemv_n_argument_errors():
         nf4_gemv_n(pt, st, xt, 64, 27648, 27648)          # more than 8 rows
     lib = _lib.load()
     w = ChrNf4Dev(64, 27648, 27648, pt.data_ptr(), st.data_ptr())
-    assert lib.chr_nf4_gemv_n_ws(w, 8) == 5 * 8 * 64       # 27648 / 6144 -> 5 slices
+    # 27 chunks of 1024 -> 3 K slices of 9; a launch carries at most 4 activation rows
+    assert lib.chr_nf4_gemv_n_ws(w, 8) == 3 * 4 * 64
+    assert lib.chr_nf4_gemv_n_ws(w, 2) == 3 * 2 * 64
     y = torch.empty(8, 64, dtype=torch.bfloat16, device="cuda")
     rc = lib.chr_nf4_gemv_n(w, xt.data_ptr(), y.data_ptr(), 8, None, None, None, 0, None)
     assert rc == -7                                         # split-K workspace missing
