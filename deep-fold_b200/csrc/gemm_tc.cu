@@ -388,14 +388,8 @@ int launch(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y, int
           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
     return kLaunch;
   }
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem_bytes(BN)) != cudaSuccess) {
-      return kLaunch;
-    }
-    attr_done = true;
-  }
+  static int attr_done[64] = {};  // per device
+  if (!ensure_smem_attr(gemm_tc_kernel<BN>, smem_bytes(BN), attr_done)) return kLaunch;
   const dim3 grid(static_cast<unsigned>(p.grid_x), static_cast<unsigned>(p.grid_y));
   gemm_tc_kernel<BN><<<grid, tThreads, smem_bytes(BN), st>>>(
       map, w.scale, x, y, partial, w.M, w.K, w.K_pad, N, p.n_ktiles, p.tiles_per_split);
@@ -765,14 +759,8 @@ int launch_rows(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y
       return kLaunch;
     }
   }
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(gemm_rows_kernel<BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             rows_smem_bytes(BN, MT)) != cudaSuccess) {
-      return kLaunch;
-    }
-    attr_done = true;
-  }
+  static int attr_done[64] = {};  // per device
+  if (!ensure_smem_attr(gemm_rows_kernel<BN, MT>, rows_smem_bytes(BN, MT), attr_done)) return kLaunch;
   const dim3 grid(static_cast<unsigned>(p.grid_x), static_cast<unsigned>(p.grid_y),
                   static_cast<unsigned>(p.split));
   gemm_rows_kernel<BN, MT><<<grid, rThreads, rows_smem_bytes(BN, MT), st>>>(

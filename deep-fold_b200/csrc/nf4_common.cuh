@@ -93,14 +93,15 @@ inline bool ensure_smem_attr(Kernel kernel, int bytes, int (&done)[64]) {
 }
 
 inline int sm_count() {
-  static int cached = 0;
-  if (cached > 0) return cached;
+  // per device: a process may drive GPUs of different sizes
+  static int cached[64] = {};
   int dev = 0, n = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess ||
-      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] > 0) return cached[dev];
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) {
     return 148;
   }
-  cached = n;
+  cached[dev] = n;
   return n;
 }
 
