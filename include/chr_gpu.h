@@ -159,13 +159,15 @@ int chr_nf4_gemv_f32(const chr_nf4_dev_t *w, const void *x, float *y, void *stre
 
 /* GEMV for N = 1..8 activation rows on CUDA cores: y_rows[n, :] = bf16( dequant(W) .
  * x_rows[n, :] (+ bias) (+ add_rows[n, :]) ) with the numerics of chr_nf4_gemv (FP32
- * weights LUT*scale, never rounded to bf16; FP32 accumulation; one rounding). Every
- * packed weight is read from HBM once and dequantized once for all N rows, which is
- * what batched decode wants where the tensor-core GEMM's bf16 weights are not.
+ * weights LUT*scale, never rounded to bf16; FP32 accumulation; one rounding). A pass
+ * over the weights serves up to four rows (every packed weight is read from HBM once
+ * and looked up once for all of them); five to eight rows take two passes. It is what
+ * batched decode wants where the tensor-core GEMM's bf16 weights are not.
  * x_rows bf16 [N, K]; y_rows bf16 [N, M]; add_rows optional bf16 [N, M] (may alias
- * y_rows); bias optional bf16 [M]. Large K is cut into slices whose FP32 partials go
- * to ws ([slices, N, M]); chr_nf4_gemv_n_ws says how many floats that takes (0 when
- * one slice covers K); a missing or small ws -> -7; N outside 1..8 -> -2.
+ * y_rows); bias optional bf16 [M]. K beyond 11264 is cut into slices whose FP32
+ * partials go to ws ([slices, min(N, 4), M], reused by the second pass);
+ * chr_nf4_gemv_n_ws says how many floats that takes (0 when one slice covers K); a
+ * missing or small ws -> -7; N outside 1..8 -> -2.
  * No counterpart in the reference (its GEMV is N = 1, gpu/nf4/nf4_gemv.cu:291-324). */
 int64_t chr_nf4_gemv_n_ws(const chr_nf4_dev_t *w, int32_t N);
 int chr_nf4_gemv_n(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows, int32_t N,

@@ -5,7 +5,7 @@ inputs (the "kernel to beat" of the decode GEMV family: gpu/nf4/nf4_gemv.cu:291-
 Each launch reads rotated weight copies larger than L2 (as gpu/nf4/bench_gemv.py:34-50
 does), is captured in a CUDA graph and timed with CUDA events. The results of both
 libraries must agree within the GEMV tolerance, this library must not be slower, and the
-numbers are written to ``gpurun_out/kernel_to_beat.json``.
+numbers are written to ``kernel_to_beat.json`` in the run's output folder.
 """
 
 from __future__ import annotations
