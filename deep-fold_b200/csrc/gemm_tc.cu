@@ -435,8 +435,9 @@ template <int BN, int MT>
 __global__ void __launch_bounds__(rThreads, 1)
 gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
                  const __grid_constant__ CUtensorMap x_map, const uint16_t *__restrict__ scale,
-                 __nv_bfloat16 *__restrict__ y, float *__restrict__ partial, int M, int K,
-                 int K_pad, int N, int n_ktiles, int tiles_per_split) {
+                 __nv_bfloat16 *y, float *__restrict__ partial, const __nv_bfloat16 *__restrict__ bias,
+                 const __nv_bfloat16 *add, int M, int K, int K_pad, int N, int n_ktiles,
+                 int tiles_per_split) {
   constexpr int kStages = rows_stages(BN, MT);
   constexpr int kBBytes = BN * tBK * 2;
   constexpr int kABytes = MT * tABytes;
@@ -650,6 +651,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
       const int c_begin = g_begin - ti * BN;
       const int c_end = col_group < kGroups ? c_begin + kPerGroup : c_begin;
       const int row = m0 + ti * tBM + quad * 32 + lane;
+      const float bias_row = (bias != nullptr && row < M) ? __bfloat162float(bias[row]) : 0.f;
       for (int c0 = c_begin; c0 < c_end; c0 += 16) {
         uint32_t v[16];
         tmem_ld16(tmem_d + (static_cast<uint32_t>(quad * 32) << 16) + ti * kAccCols + c0, v);
@@ -663,7 +665,10 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
               if (partial != nullptr) {
                 partial[(static_cast<size_t>(blockIdx.z) * N + n) * M + row] = f;
               } else {
-                y[static_cast<size_t>(n) * M + row] = __float2bfloat16(f);
+                // bias and residual join the FP32 sum before its one rounding
+                float out = f + bias_row;
+                if (add != nullptr) out += __bfloat162float(add[static_cast<size_t>(n) * M + row]);
+                y[static_cast<size_t>(n) * M + row] = __float2bfloat16(out);
               }
             }
           }
@@ -679,12 +684,16 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap packed_map,
   }
 }
 
-__global__ void reduce_rows_kernel(const float *__restrict__ partial, __nv_bfloat16 *__restrict__ y,
-                                   long long total, int splits) {
+// y[n, m] = bf16( sum of the split-K partials (in split order) + bias[m] + add[n, m] )
+__global__ void reduce_rows_kernel(const float *__restrict__ partial, __nv_bfloat16 *y,
+                                   const __nv_bfloat16 *__restrict__ bias, const __nv_bfloat16 *add,
+                                   long long total, int splits, int M) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
   float v = 0.f;
   for (int s = 0; s < splits; ++s) v += partial[static_cast<size_t>(s) * total + i];
+  if (bias != nullptr) v += __bfloat162float(bias[i % M]);
+  if (add != nullptr) v += __bfloat162float(add[i]);
   y[i] = __float2bfloat16(v);
 }
 
@@ -733,7 +742,8 @@ RowsPlan plan_rows(int M, int K_pad, int N, bool have_ws) {
 
 template <int BN, int MT = 1>
 int launch_rows(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y, int N,
-                float *partial, const RowsPlan &p, cudaStream_t st) {
+                float *partial, const __nv_bfloat16 *bias, const __nv_bfloat16 *add, const RowsPlan &p,
+                cudaStream_t st) {
   EncodeTiled enc = encode_fn();
   if (enc == nullptr) return kLaunch;
   CUtensorMap wmap, xmap;
@@ -764,11 +774,11 @@ int launch_rows(const chr_nf4_dev_t &w, const __nv_bfloat16 *x, __nv_bfloat16 *y
   const dim3 grid(static_cast<unsigned>(p.grid_x), static_cast<unsigned>(p.grid_y),
                   static_cast<unsigned>(p.split));
   gemm_rows_kernel<BN, MT><<<grid, rThreads, rows_smem_bytes(BN, MT), st>>>(
-      wmap, xmap, w.scale, y, partial, w.M, w.K, w.K_pad, N, p.n_ktiles, p.tiles_per_split);
+      wmap, xmap, w.scale, y, partial, bias, add, w.M, w.K, w.K_pad, N, p.n_ktiles, p.tiles_per_split);
   if (partial != nullptr) {
     const long long total = static_cast<long long>(w.M) * N;
-    reduce_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(partial, y, total,
-                                                                                   p.split);
+    reduce_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
+        partial, y, bias, add, total, p.split, w.M);
   }
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunch;
 }
@@ -815,8 +825,9 @@ extern "C" int64_t chr_nf4_gemm_rows_ws(const chr_nf4_dev_t *w, int32_t N) {
   return chr::plan_rows(w->M, w->K_pad, N, true).ws_floats;
 }
 
-extern "C" int chr_nf4_gemm_rows(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows,
-                                 int32_t N, float *ws, int64_t ws_floats, void *stream) {
+extern "C" int chr_nf4_gemm_rows_add(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows,
+                                     int32_t N, const void *bias, const void *add_rows, float *ws,
+                                     int64_t ws_floats, void *stream) {
   using namespace chr;
   if (x_rows == nullptr || y_rows == nullptr) return kNull;
   const int rc = check_matrix(w);
@@ -833,13 +844,20 @@ extern "C" int chr_nf4_gemm_rows(const chr_nf4_dev_t *w, const void *x_rows, voi
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto *xb = static_cast<const __nv_bfloat16 *>(x_rows);
   auto *yb = static_cast<__nv_bfloat16 *>(y_rows);
+  auto *bb = static_cast<const __nv_bfloat16 *>(bias);
+  auto *ab = static_cast<const __nv_bfloat16 *>(add_rows);
   switch (p.bn) {
-    case 16: return launch_rows<16>(*w, xb, yb, N, partial, p, st);
-    case 32: return launch_rows<32>(*w, xb, yb, N, partial, p, st);
-    case 64: return launch_rows<64>(*w, xb, yb, N, partial, p, st);
-    case 128: return launch_rows<128>(*w, xb, yb, N, partial, p, st);
+    case 16: return launch_rows<16>(*w, xb, yb, N, partial, bb, ab, p, st);
+    case 32: return launch_rows<32>(*w, xb, yb, N, partial, bb, ab, p, st);
+    case 64: return launch_rows<64>(*w, xb, yb, N, partial, bb, ab, p, st);
+    case 128: return launch_rows<128>(*w, xb, yb, N, partial, bb, ab, p, st);
     default:
-      if (p.mt == 2) return launch_rows<256, 2>(*w, xb, yb, N, partial, p, st);
-      return launch_rows<256>(*w, xb, yb, N, partial, p, st);
+      if (p.mt == 2) return launch_rows<256, 2>(*w, xb, yb, N, partial, bb, ab, p, st);
+      return launch_rows<256>(*w, xb, yb, N, partial, bb, ab, p, st);
   }
+}
+
+extern "C" int chr_nf4_gemm_rows(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows,
+                                 int32_t N, float *ws, int64_t ws_floats, void *stream) {
+  return chr_nf4_gemm_rows_add(w, x_rows, y_rows, N, nullptr, nullptr, ws, ws_floats, stream);
 }

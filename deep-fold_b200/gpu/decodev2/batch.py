@@ -114,15 +114,10 @@ def _linear(mat: DeviceLinear, rows: torch.Tensor, out: torch.Tensor | None = No
     if n <= GEMV_ROWS:
         return nf4_gemv_n(mat.packed, mat.scale, rows, mat.M, mat.K, mat.K_pad, out=out, add=add,
                           bias=mat.bias)
-    y = nf4_gemm_rows(mat.packed, mat.scale, rows, mat.M, mat.K, mat.K_pad)
-    if mat.bias is not None:
-        y = y + mat.bias
-    if add is not None:
-        y = y + add
-    if out is not None:
-        out.view(n, mat.M).copy_(y)
-        return out
-    return y
+    # bias and residual ride the GEMM epilogue (one rounding); ``add`` may be ``out`` itself
+    return nf4_gemm_rows(mat.packed, mat.scale, rows, mat.M, mat.K, mat.K_pad,
+                         out=None if out is None else out.view(n, mat.M), bias=mat.bias,
+                         add=None if add is None else add.view(n, mat.M))
 
 
 def batched_forward(state: BatchState, weights: DeviceWeights) -> None:
@@ -135,7 +130,14 @@ def batched_forward(state: BatchState, weights: DeviceWeights) -> None:
     state.valid_len.add_(1)
     for li, layer in enumerate(weights.layers):
         h = nf4_rms_rows(state.x, layer.norm1, spec.rms_eps)
-        if layer.wqkv is None:
+        if layer.wqkv is None and layer.qkv_rows is not None:
+            # q, k, v stacked in memory: one pass over the activations instead of three
+            y = _linear(layer.qkv_rows, h)
+            mq, mk = layer.q.M, layer.k.M
+            state.q.view(b, -1).copy_(y[:, :mq])
+            state.k_act.view(b, -1).copy_(y[:, mq:mq + mk])
+            state.v_act.view(b, -1).copy_(y[:, mq + mk:])
+        elif layer.wqkv is None:
             _linear(layer.q, h, out=state.q)
             _linear(layer.k, h, out=state.k_act)
             _linear(layer.v, h, out=state.v_act)

@@ -106,8 +106,10 @@ class DeviceLinear:
         return int(self.packed.numel()) + 2 * int(self.scale.numel())
 
 
-def nf4_linear(mat: DeviceLinear, x: torch.Tensor) -> torch.Tensor:
-    """``x`` ``[N, K]`` -> ``[N, M]`` bf16 on ``x.device`` (+ bias)."""
+def nf4_linear(mat: DeviceLinear, x: torch.Tensor, add: torch.Tensor | None = None) -> torch.Tensor:
+    """``x`` ``[N, K]`` -> ``[N, M]`` bf16 on ``x.device`` (+ bias) (+ ``add`` ``[N, M]``). On the
+    wide-GEMM path bias and ``add`` are folded into the epilogue (one rounding); elsewhere they
+    are added as tensor ops."""
     if x.shape[-1] != mat.K:
         raise ValueError(f"x K={x.shape[-1]} != {mat.K}")
     if x.device.type != "cuda":
@@ -121,7 +123,12 @@ def nf4_linear(mat: DeviceLinear, x: torch.Tensor) -> torch.Tensor:
     elif n == 1:
         y = nf4_gemm(mat.packed, mat.scale, rows.reshape(mat.K), mat.M, mat.K, mat.K_pad).view(1, mat.M)
     elif _ROWS_GEMM and mat.K % 8 == 0:
-        y = nf4_gemm_rows(mat.packed, mat.scale, rows.contiguous(), mat.M, mat.K, mat.K_pad)
+        fused_add = None
+        if add is not None and add.dtype is torch.bfloat16:
+            fused_add = add.reshape(n, mat.M).contiguous()
+        y = nf4_gemm_rows(mat.packed, mat.scale, rows.contiguous(), mat.M, mat.K, mat.K_pad,
+                          bias=mat.bias, add=fused_add)
+        return y if add is None or fused_add is not None else y + add.reshape(n, mat.M).to(y.dtype)
     else:
         cols = []
         for lo in range(0, n, LIVE_MAX_N):
@@ -130,6 +137,8 @@ def nf4_linear(mat: DeviceLinear, x: torch.Tensor) -> torch.Tensor:
         y = (cols[0] if len(cols) == 1 else torch.cat(cols, dim=1)).t().contiguous()
     if mat.bias is not None:
         y = y + mat.bias.to(dtype=y.dtype)
+    if add is not None:
+        y = y + add.reshape(n, mat.M).to(dtype=y.dtype)
     return y
 
 

@@ -119,7 +119,10 @@ def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch
             k = apply_rope_torch(k, cos, sin)
             state.kv.write_range(li, start, k, v)
         attn = _attend(q.contiguous(), state.kv.k[li], state.kv.v[li], spec, start)
-        x = x + _reduced(state, nf4_linear(layer.o, attn))
+        if spec.tp == 1:
+            x = nf4_linear(layer.o, attn, add=x)      # residual folded into the GEMM epilogue
+        else:
+            x = x + _reduced(state, nf4_linear(layer.o, attn))
         if fused:
             h = nf4_rms_rows(x, layer.norm2, spec.rms_eps)
         else:
@@ -130,7 +133,10 @@ def forward_prefill(state: DecodeState, weights: DeviceWeights, token_ids: torch
                    else F.silu(gu[:, : layer.gate.M]) * gu[:, layer.gate.M:])
         else:
             act = F.silu(nf4_linear(layer.gate, h)) * nf4_linear(layer.up, h)
-        x = x + _reduced(state, nf4_linear(layer.down, act))
+        if spec.tp == 1:
+            x = nf4_linear(layer.down, act, add=x)
+        else:
+            x = x + _reduced(state, nf4_linear(layer.down, act))
     state.position.fill_(seq)
     state.valid_len.fill_(seq)
     if not logits:

@@ -186,11 +186,15 @@ def nf4_gemm_rows(
     K: int,  # noqa: N803
     K_pad: int,  # noqa: N803
     out: torch.Tensor | None = None,
+    bias: torch.Tensor | None = None,
+    add: torch.Tensor | None = None,
 ) -> torch.Tensor:
-    """``y[N, M] = x_rows[N, K] @ dequant(W).T`` on the tensor cores, any ``N >= 1``.
+    """``y[N, M] = x_rows[N, K] @ dequant(W).T (+ bias[M]) (+ add[N, M])`` on the tensor
+    cores, any ``N >= 1``; bias and residual join the FP32 sum before its one rounding.
 
-    Activations keep their natural ``[tokens, features]`` layout on both sides.
-    Needs ``K % 8 == 0`` (TMA row pitch); other shapes go through :func:`nf4_gemm`.
+    Activations keep their natural ``[tokens, features]`` layout on both sides; ``add``
+    may alias ``out``. Needs ``K % 8 == 0`` (TMA row pitch); other shapes go through
+    :func:`nf4_gemm`.
     """
     if not x_rows.is_cuda or x_rows.dtype is not torch.bfloat16:
         _fail("x_rows must be CUDA bfloat16")
@@ -210,8 +214,16 @@ def nf4_gemm_rows(
     lib = _lib.load()
     need = int(lib.chr_nf4_gemm_rows_ws(ctypes.byref(dev), n))
     ws = torch.empty(need, dtype=torch.float32, device=x_rows.device) if need > 0 else None
-    rc = lib.chr_nf4_gemm_rows(ctypes.byref(dev), _ptr(x_rows), _ptr(out), n, _ptr(ws), need, _stream())
-    _lib.check(rc, "chr_nf4_gemm_rows")
+    bias_t = _opt_bf16(bias, int(M), "bias", exact=True)
+    add_t = None
+    if add is not None:
+        if (not add.is_cuda or add.dtype is not torch.bfloat16 or not add.is_contiguous()
+                or add.numel() != n * int(M)):
+            _fail("add must be contiguous CUDA bfloat16 [N, M]")
+        add_t = add
+    rc = lib.chr_nf4_gemm_rows_add(ctypes.byref(dev), _ptr(x_rows), _ptr(out), n, _ptr(bias_t),
+                                   _ptr(add_t), _ptr(ws), need, _stream())
+    _lib.check(rc, "chr_nf4_gemm_rows_add")
     del keep
     return out
 

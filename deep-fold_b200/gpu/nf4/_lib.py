@@ -120,6 +120,9 @@ SIGNATURES = {
     "chr_nf4_gemm_rows": (
         c_int, [_DEV, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p]
     ),
+    "chr_nf4_gemm_rows_add": (
+        c_int, [_DEV, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
+    ),
     "chr_nf4_embed_rows": (
         c_int, [_DEV, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     ),

@@ -245,6 +245,16 @@ int64_t chr_nf4_gemm_rows_ws(const chr_nf4_dev_t *w, int32_t N);
 int chr_nf4_gemm_rows(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows, int32_t N,
                       float *ws, int64_t ws_floats, void *stream);
 
+/* chr_nf4_gemm_rows with the bias and a residual folded into the epilogue:
+ *   y_rows[n, m] = bf16( sum_k ... + f32(bias[m]) + f32(add_rows[n, m]) )
+ * one rounding instead of one per torch op (the reference adds bias and residual as
+ * bf16 tensor ops after the GEMM, gpu/decodev2/linear.py:131-133,
+ * gpu/decodev2/prefill.py:118-131). bias: optional bf16 [M]; add_rows: optional bf16
+ * [N, M], may alias y_rows. With split-K the reduction kernel does the adding. */
+int chr_nf4_gemm_rows_add(const chr_nf4_dev_t *w, const void *x_rows, void *y_rows, int32_t N,
+                          const void *bias, const void *add_rows, float *ws, int64_t ws_floats,
+                          void *stream);
+
 /* Programmatic dependent launch for the decode-chain kernels (GEMV family,
  * attention, embedding rows, pick): on (default, or CHR_NF4_PDL=1) lets a kernel's
  * prologue overlap the previous kernel's tail, inside CUDA graphs as well; 0

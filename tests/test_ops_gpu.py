@@ -404,6 +404,30 @@ def test_gemm_rows_matches_oracle(m, k, n):
     assert nf4_gemm_status() == 0
 
 
+@pytest.mark.parametrize("m,k,n", [(2048, 2048, 37), (5120, 13824, 64), (300, 1000, 5), (22016, 2048, 512)])
+def test_gemm_rows_bias_and_residual_ride_the_epilogue(m, k, n):
+    """``chr_nf4_gemm_rows_add``: bias[m] and add[n, m] join the FP32 sum before its one rounding,
+    with and without split-K, and with the residual aliasing the output."""
+    from gpu.nf4 import nf4_gemm_rows
+
+    rng = np.random.default_rng(m + k + n)
+    kp = o.padded_k(k)
+    p, s, pt, st = blobs(m, k, 21, weight_like=True)
+    xt = torch.from_numpy(rng.standard_normal((n, k)).astype(np.float32)).to(torch.bfloat16).to(DEV)
+    bt, bf = bf16_vec(rng, m, std=0.05)
+    at, af = bf16_vec(rng, n, m, std=0.5)
+    plain = nf4_gemm_rows(pt, st, xt, m, k, kp).float()
+    want = plain + bt.float()[None, :] + at.float()
+    got = nf4_gemm_rows(pt, st, xt, m, k, kp, bias=bt, add=at)
+    # the fused result is the unrounded sum rounded once: within one bf16 ulp of the
+    # twice-rounded reference, plus the rounding of `plain` itself
+    tol = 2.0 ** -7 * want.abs().max().item()
+    assert (got.float() - want).abs().max().item() <= tol
+    dest = at.clone()
+    nf4_gemm_rows(pt, st, xt, m, k, kp, out=dest, bias=bt, add=dest)
+    assert torch.equal(dest, got)
+
+
 def test_gemm_rows_rejects_unaligned_k():
     from gpu.nf4 import nf4_gemm_rows
 
