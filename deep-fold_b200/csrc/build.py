@@ -26,7 +26,7 @@ OBJ_DIR = CSRC / "build"
 CUDA_SOURCES = ("gemv.cu", "decode_ops.cu", "prefill_ops.cu", "prefill_attn.cu", "gemm.cu", "gemm_tc.cu", "codec_dev.cu",
                 "version.cu")
 CXX_SOURCES = ("codec.cpp",)
-HEADERS = ("nf4_common.cuh", "gemv_ring.cuh", "gemv_cols.cuh", "gemv_n.cuh", "attn_core.cuh", "gemm_plan.h")
+HEADERS = ("nf4_common.cuh", "gemv_ring.cuh", "gemv_cols.cuh", "gemv_n.cuh", "attn_core.cuh", "attn_mma.cuh", "gemm_plan.h")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

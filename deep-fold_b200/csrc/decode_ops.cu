@@ -6,7 +6,7 @@
 // (kv head, sequence split) pair and serves every query head of that kv head, so
 // a cache row is read once per group instead of once per query head.
 
-#include "attn_core.cuh"
+#include "attn_mma.cuh"
 
 namespace chr {
 namespace {
@@ -128,11 +128,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_split_kernel(const AttnA
 // The same items for B sequences in one launch: grid.y = B * n_kv; every sequence has
 // its own q, current k/v, cache, output, split partials, valid length and position
 // (consecutive blocks of the per-sequence sizes).
-struct AttnBatch {
-  int batch;
-  long long q_stride, kv_act_stride, cache_stride, out_stride, ws_stride;
-};
-
 template <int P, int H>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_batch_kernel(const AttnArgs proto,
                                                                  const AttnBatch bt) {
@@ -156,6 +151,75 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_batch_kernel(const AttnA
   if (a.position != nullptr) a.position += b;
   unsigned int *ctr = &g_attn_arrivals[(blockIdx.y * gridDim.z + blockIdx.z) % kMaxAttnGroups];
   attn_item<P, H>(a, sm, blockIdx.x, kvh, blockIdx.z, ctr, threadIdx.x, [] { __syncthreads(); });
+}
+
+// Tensor-core form (attn_mma.cuh) for head dims 16 / 32 / 64 / 128, one sequence or B.
+// Grid: (splits, B * kv heads, head chunks of 8).
+template <int HD>
+__global__ void __launch_bounds__(kMmaThreads, 1) attn_mma_kernel(const AttnArgs proto,
+                                                                const AttnBatch bt) {
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  pdl_trigger();
+  pdl_wait();  // q, k_act, v_act, position and valid_len come from earlier kernels
+  const int b = blockIdx.y / proto.n_kv;
+  const int kvh = blockIdx.y - b * proto.n_kv;
+  AttnArgs a = proto;
+  a.q += b * bt.q_stride;
+  if (a.k_act != nullptr) a.k_act += b * bt.kv_act_stride;
+  if (a.v_act != nullptr) a.v_act += b * bt.kv_act_stride;
+  a.k_cache += b * bt.cache_stride;
+  a.v_cache += b * bt.cache_stride;
+  a.out += b * bt.out_stride;
+  a.m_s += b * bt.ws_stride;
+  a.l_s += b * bt.ws_stride;
+  a.o_s += b * bt.ws_stride;
+  a.valid_len += b;
+  if (a.position != nullptr) a.position += b;
+  unsigned int *ctr = &g_attn_arrivals[(blockIdx.y * gridDim.z + blockIdx.z) % kMaxAttnGroups];
+  attn_mma_item<HD>(a, attn_smem, blockIdx.x, kvh, blockIdx.z, ctr);
+}
+
+// CHR_NF4_ATTN=simt keeps every head dim on the CUDA-core form (A/B runs).
+static bool attn_mma_wanted(int hd) {
+  static int simt = -1;
+  if (simt < 0) {
+    const char *env = std::getenv("CHR_NF4_ATTN");
+    simt = (env != nullptr && env[0] == 's') ? 1 : 0;
+  }
+  return simt == 0 && (hd == 16 || hd == 32 || hd == 64 || hd == 128);
+}
+
+template <int HD>
+static cudaError_t launch_attn_mma_hd(const AttnArgs &a, const AttnBatch &bt, dim3 grid, cudaStream_t st) {
+  static int done[64] = {};
+  if (!ensure_smem_attr(attn_mma_kernel<HD>, AttnMmaLayout<HD>::kBytes, done)) return cudaErrorInvalidValue;
+  return launch_chain(attn_mma_kernel<HD>, grid, dim3(kMmaThreads), AttnMmaLayout<HD>::kBytes, st, a, bt);
+}
+
+// `a.n_split` is the caller's count on entry; the count used is written back into it
+// (and the workspace pointers follow it).
+static int launch_attn_mma(AttnArgs a, AttnBatch bt, float *ws, int n_split, cudaStream_t st) {
+  const int n_rep = a.n_q / a.n_kv;
+  const int chunks = (n_rep + kMmaHeads - 1) / kMmaHeads;
+  const long long groups = static_cast<long long>(bt.batch) * a.n_kv * chunks;
+  if (groups > kMaxAttnGroups) return kDims;
+  n_split = attn_splits_used(n_split, groups);
+  const int slots = a.n_q * n_split;
+  a.n_split = n_split;
+  a.m_s = ws;
+  a.l_s = ws + slots;
+  a.o_s = ws + 2 * slots;
+  bt.ws_stride = static_cast<long long>(slots) * (a.hd + 2);
+  const dim3 grid(static_cast<unsigned>(n_split), static_cast<unsigned>(bt.batch * a.n_kv),
+                  static_cast<unsigned>(chunks));
+  cudaError_t e;
+  switch (a.hd) {
+    case 16: e = launch_attn_mma_hd<16>(a, bt, grid, st); break;
+    case 32: e = launch_attn_mma_hd<32>(a, bt, grid, st); break;
+    case 64: e = launch_attn_mma_hd<64>(a, bt, grid, st); break;
+    default: e = launch_attn_mma_hd<128>(a, bt, grid, st); break;
+  }
+  return e == cudaSuccess ? kOk : kLaunch;
 }
 
 // ----------------------------------------------------------------------------
@@ -391,6 +455,7 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The workspace is sized for the caller's n_split; fewer splits may be used.
   const int n_rep = n_q / n_kv;
+  const int n_split_asked = n_split;
   n_split = attn_splits_used(n_split, n_kv * attn_head_chunks(n_rep, hd));
   const int slots = n_q * n_split;
   AttnArgs a{};
@@ -416,6 +481,11 @@ extern "C" int chr_nf4_attn(const void *q, const void *k, const void *v, void *o
   a.max_seq = max_seq;
   a.scale = scale;
 
+  if (attn_mma_wanted(hd) && aligned(k, 16) && aligned(v, 16)) {
+    AttnBatch one{};
+    one.batch = 1;
+    return launch_attn_mma(a, one, ws, n_split_asked, st);
+  }
   const int heads = attn_heads_per_item(n_rep, hd);
   const int head_chunks = (n_rep + heads - 1) / heads;
   if (n_kv * head_chunks > kMaxAttnGroups) return kDims;
@@ -451,6 +521,7 @@ extern "C" int chr_nf4_attn_batch(const void *q, const void *k, const void *v, v
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int n_rep = n_q / n_kv;
+  const int n_split_asked = n_split;
   n_split = attn_splits_used(n_split, batch * n_kv * attn_head_chunks(n_rep, hd));
   const int slots = n_q * n_split;
   AttnArgs a{};
@@ -482,6 +553,10 @@ extern "C" int chr_nf4_attn_batch(const void *q, const void *k, const void *v, v
   bt.cache_stride = static_cast<long long>(max_seq) * n_kv * hd;
   bt.out_stride = static_cast<long long>(n_q) * hd;
   bt.ws_stride = static_cast<long long>(slots) * (hd + 2);
+  if (attn_mma_wanted(hd) && aligned(k, 16) && aligned(v, 16) &&
+      (bt.cache_stride * 2) % 16 == 0) {
+    return launch_attn_mma(a, bt, ws, n_split_asked, st);
+  }
   const int heads = attn_heads_per_item(n_rep, hd);
   const int chunks = (n_rep + heads - 1) / heads;
   if (static_cast<long long>(batch) * n_kv * chunks > kMaxAttnGroups) return kDims;
