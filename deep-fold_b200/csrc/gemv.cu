@@ -113,47 +113,71 @@ nf4_gemv_ar_kernel(const GemvArgs a, const PeerArgs pa) {
   // peer is gone: do not spend the full poll budget again on every call
   const bool give_up = *reinterpret_cast<volatile int *>(pa.status) != 0;
 
-  // Rows of this CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of G*R rows. All of
-  // them are exchanged in one pass, a row per thread, so that the round trips overlap.
+  // Rows of this CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of G*R rows. They
+  // are exchanged with one thread per (row, peer), so that neither the peer stores nor
+  // the polls of a row queue up behind each other (a thread per row polling its peers
+  // one after the other cost about 0.6 us per peer at 8 GPUs); the peers' values meet
+  // in shared memory, where a thread per row sums them in rank order.
   const int rt = a.G * R;
   const int my_tiles = blockIdx.x < a.n_tiles ? (a.n_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+  const int n_rows_cta = my_tiles * rt;
+  const int others = pa.world - 1;
+  constexpr int kArChunk = 1024;  // rows per pass through the gather buffer
+  float *gather = reinterpret_cast<float *>(smem + kHeadBytes);  // [rows][others]; the ring is idle now
+  auto row_of = [&](int i) { return (blockIdx.x + (i / rt) * gridDim.x) * rt + i % rt; };
   __nv_bfloat16 *y = a.y[0];
-  for (int idx = tid; idx < my_tiles * rt; idx += blockDim.x) {
-    const int row = (blockIdx.x + (idx / rt) * gridDim.x) * rt + idx % rt;
-    if (row >= M) continue;
-    const float own = __ldcg(mine + row);
+  for (int c0 = 0; c0 < n_rows_cta; c0 += kArChunk) {
+    const int cn = min(kArChunk, n_rows_cta - c0);
     // 1. push (value, epoch) into every peer's slot for this rank
-    for (int p = 0; p < pa.world; ++p) {
-      if (p != pa.rank) {
+    for (int idx = tid; idx < cn * others; idx += blockDim.x) {
+      const int i = idx / others;
+      const int j = idx - i * others;
+      const int p = j < pa.rank ? j : j + 1;
+      const int row = row_of(c0 + i);
+      if (row < M) {
+        const float own = __ldcg(mine + row);
         asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(slot_of(p, e, pa.rank) + row),
                      "r"(__float_as_uint(own)), "r"(e)
                      : "memory");
       }
     }
-    // 2. collect the peers' words for the same row, summing in rank order
-    float v = 0.f;
-    for (int r = 0; r < pa.world; ++r) {
-      if (r == pa.rank) {
-        v += own;
-        continue;
-      }
-      const uint2 *src = slot_of(pa.rank, e, r) + row;
-      uint32_t bits = 0u, seen = 0u;
-      unsigned int polls = 0;
-      for (;;) {
-        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(seen) : "l"(src)
-                     : "memory");
-        if (seen == e || give_up) break;
-        if (++polls >= pa.polls) {
-          atomicExch(pa.status, 1);
-          break;
+    // 2. collect the peers' words (bounded polls; a word that never comes counts as 0)
+    for (int idx = tid; idx < cn * others; idx += blockDim.x) {
+      const int i = idx / others;
+      const int j = idx - i * others;
+      const int p = j < pa.rank ? j : j + 1;
+      const int row = row_of(c0 + i);
+      float got = 0.f;
+      if (row < M) {
+        const uint2 *src = slot_of(pa.rank, e, p) + row;
+        uint32_t bits = 0u, seen = 0u;
+        unsigned int polls = 0;
+        for (;;) {
+          asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(seen) : "l"(src)
+                       : "memory");
+          if (seen == e || give_up) break;
+          if (++polls >= pa.polls) {
+            atomicExch(pa.status, 1);
+            break;
+          }
         }
+        got = seen == e ? __uint_as_float(bits) : 0.f;
       }
-      v += seen == e ? __uint_as_float(bits) : 0.f;
+      gather[idx] = got;
     }
-    // 3. add the residual, round once
-    v += __bfloat162float(y[row]);
-    y[row] = __float2bfloat16(v);
+    __syncthreads();
+    // 3. rank-ordered sum, residual, one rounding
+    for (int i = tid; i < cn; i += blockDim.x) {
+      const int row = row_of(c0 + i);
+      if (row >= M) continue;
+      float v = 0.f;
+      for (int r = 0; r < pa.world; ++r) {
+        v += r == pa.rank ? __ldcg(mine + row) : gather[i * others + (r < pa.rank ? r : r - 1)];
+      }
+      v += __bfloat162float(y[row]);
+      y[row] = __float2bfloat16(v);
+    }
+    __syncthreads();
   }
   // 4. the last CTA out publishes the new epoch
   __syncthreads();
