@@ -238,6 +238,9 @@ class _Spec:
 @pytest.mark.parametrize("n_q,n_kv,hd,max_seq,vl", [
     (16, 2, 128, 2048, 513), (40, 8, 128, 1024, 1024), (48, 8, 128, 256, 1), (4, 2, 16, 16, 5),
     (8, 2, 64, 32, 32), (8, 8, 256, 64, 40), (40, 8, 128, 512, 0), (12, 1, 128, 128, 77),
+    # the tensor-core form's 128-row tiles: exactly one, one row over, one short of two,
+    # many tiles per split, and a group of seven heads
+    (40, 8, 128, 256, 128), (40, 8, 128, 256, 129), (7, 1, 64, 300, 255), (16, 2, 32, 4608, 4500),
 ])
 def test_attention_plain_matches_oracle(n_q, n_kv, hd, max_seq, vl):
     from gpu.nf4 import ATTN_SPLIT, nf4_attn
@@ -262,7 +265,9 @@ def test_attention_plain_matches_oracle(n_q, n_kv, hd, max_seq, vl):
 
 
 @pytest.mark.parametrize("n_q,n_kv,hd,max_seq,pos", [(16, 2, 128, 2048, 512), (40, 8, 128, 64, 0),
-                                                      (4, 2, 16, 16, 15), (8, 2, 64, 32, 9)])
+                                                      (4, 2, 16, 16, 15), (8, 2, 64, 32, 9),
+                                                      # the current row is the last / the first row of a tile
+                                                      (40, 8, 128, 256, 127), (40, 8, 128, 256, 128)])
 def test_attention_fused_rope_and_cache_write(n_q, n_kv, hd, max_seq, pos):
     from gpu.nf4 import ATTN_SPLIT, nf4_attn, nf4_rope_kv
 
