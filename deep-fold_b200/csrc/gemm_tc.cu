@@ -25,6 +25,8 @@
 
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "gemm_plan.h"
 #include <cstdlib>
 
@@ -726,14 +728,31 @@ RowsPlan plan_rows(int M, int K_pad, int N, bool have_ws) {
   }
   p.grid_x = (M + tBM * p.mt - 1) / (tBM * p.mt);
   p.n_ktiles = (K_pad + tBK - 1) / tBK;
+  // Split-K: with fewer CTAs than a few waves, cutting K lets a launch fill the SMs. The
+  // count is chosen by a small cost model, not by "one full wave": 80 CTAs cut in two are
+  // 160 CTAs = two waves on 148 SMs, no faster than one. Cost in microseconds: waves x
+  // K tiles per CTA x time per K tile (tensor-bound at wide N, dequant-bound below) + the
+  // reduction kernel (a launch and split x M x N floats of traffic).
   int want = 1;
   if (have_ws) {
     const int ctas = p.grid_x * p.grid_y;
-    want = (sm_count() + ctas - 1) / ctas;          // one full wave
-    const int cap = p.n_ktiles / 4 > 0 ? p.n_ktiles / 4 : 1;  // at least four K tiles per split
-    if (want > cap) want = cap;
+    const int sms = sm_count();
+    const double t_tile = std::max(0.30, 2.0 * tBM * p.mt * p.bn * tBK / 9.4e6);
+    const int cap = p.n_ktiles / 8 > 0 ? p.n_ktiles / 8 : 1;  // at least eight K tiles per split
+    double best = 0.0;
+    for (int sp = 1; sp <= cap && sp <= 16; ++sp) {
+      const int tiles = (p.n_ktiles + sp - 1) / sp;
+      const int real = (p.n_ktiles + tiles - 1) / tiles;
+      if (real != sp) continue;
+      const int waves = (ctas * sp + sms - 1) / sms;
+      double cost = static_cast<double>(waves) * tiles * t_tile;
+      if (sp > 1) cost += 3.0 + static_cast<double>(sp) * M * N * 4.0 / 3.0e6;
+      if (sp == 1 || cost < best) {
+        best = cost;
+        want = sp;
+      }
+    }
   }
-  if (want < 1) want = 1;
   p.tiles_per_split = (p.n_ktiles + want - 1) / want;
   p.split = (p.n_ktiles + p.tiles_per_split - 1) / p.tiles_per_split;
   p.ws_floats = p.split > 1 ? static_cast<long long>(p.split) * M * N : 0;
