@@ -746,7 +746,9 @@ RowsPlan plan_rows(int M, int K_pad, int N, bool have_ws) {
       if (real != sp) continue;
       const int waves = (ctas * sp + sms - 1) / sms;
       double cost = static_cast<double>(waves) * tiles * t_tile;
-      if (sp > 1) cost += 3.0 + static_cast<double>(sp) * M * N * 4.0 / 3.0e6;
+      // partials are written by the GEMM and read back by the reduction: 8 bytes per
+      // element and split, at the 2.5 TB/s such scattered FP32 traffic reaches
+      if (sp > 1) cost += 4.0 + static_cast<double>(sp) * M * N * 8.0 / 2.5e6;
       if (sp == 1 || cost < best) {
         best = cost;
         want = sp;
