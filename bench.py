@@ -1,11 +1,13 @@
 """Benchmark of the NF4 decode/prefill path: batch-1 greedy decode tokens/s.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--model qwen2.5-32b-arch] [--prompt 1792] [--chunk 512] [--batch B]
+                    [--model qwen2.5-32b-arch] [--prompt T] [--chunk 512] [--batch B[,B...]]
+                    [--prefill-sweep T[,T...]] [--breakdown] [--nccl] [--no-cpu]
 
 One JSON line on stdout. A "step" is one greedy decode token (one replay of the
 captured step graph) of the named random-init architecture after a prompt that
-fills the context (default: the Qwen2.5-32B architecture, 1792-token prompt, so
+fills the context (default: the Qwen2.5-32B architecture; the prompt length is the
+context minus the room the warm-up and the timed windows need, at most 1792 tokens, so
 the 128 timed steps run against a ~2k-token KV cache). ``value`` is the
 device-window rate (tokens resident, no host traffic), ``e2e`` the rate with a
 pinned-host token id copied in and the picked id read back every step.
@@ -17,7 +19,11 @@ matmul, the reference's CPU NF4 path restated) on the 4096 x 4096 layer at N = 1
 and N = 32, dequant and matmul apart, median of 5. ``--impl reference`` runs only
 the CPU path: each step is a bounded sample (a slab of one gate matrix) that is
 really timed, and the tokens/s it prints is that time scaled by the model's
-weight count.
+weight count. ``--batch`` decodes B sequences together (one line per size),
+``--prefill-sweep`` times the chunked prefill per prompt length, ``--breakdown`` adds
+the per-layer time of every operation kind; under ``torch.distributed.run`` the model is
+tensor-parallel over the ranks, ``exchange_us`` is the cost of the exchange fused into
+the row-split linears, and the ranks' first ids must agree.
 """
 
 from __future__ import annotations
