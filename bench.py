@@ -556,7 +556,7 @@ def run_ours(args, spec) -> None:
     if exchange_us is not None:
         line["exchange_us"] = exchange_us
     line["prefill_mode"] = prefill_mode
-    if not args.no_cpu:
+    if not args.no_cpu and world == 1:  # the CPU leg belongs to the one-GPU line
         line["cpu_baseline"] = cpu_baseline(full_spec)
     print(json.dumps(line), flush=True)
     if comm is not None:
