@@ -686,7 +686,10 @@ def run_batched(args, spec, weights, local: int) -> None:
         "step_frac_of_hbm_peak": step_bytes / (dev_ms / args.steps / 1e3) / 1e9 / peaks["hbm"],
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": 8 * b,
                 "d2h_bytes_per_step": 8 * b},
-        "gpu_launches": args.steps * (1 + spec.n_layers * 10 + 2 + b),
+        # this library's kernels per step, counted from below: embedding rows, per layer two
+        # row norms, four linears, attention, SiLU*up (split-K reductions not counted),
+        # final norm, lm_head, one pick
+        "gpu_launches": args.steps * (1 + spec.n_layers * 8 + 3),
         "greedy_ids_head": [int(t) for t in head[:, 0].tolist()],
         "clocks": clk,
     }

@@ -272,14 +272,12 @@ __global__ void embed_rows_kernel(const uint8_t *__restrict__ packed,
 // ----------------------------------------------------------------------------
 constexpr int kPickThreads = 256;
 
-__global__ void __launch_bounds__(kPickThreads)
-pick_commit_kernel(const __nv_bfloat16 *__restrict__ logits, int n, int64_t *next_token,
-                   int64_t *token, int64_t *position, uint8_t *finished, int64_t eos,
-                   unsigned long long *best, unsigned int *ticket) {
+__device__ __forceinline__ void pick_commit_body(const __nv_bfloat16 *__restrict__ logits, int n,
+                                                 int64_t *next_token, int64_t *token,
+                                                 int64_t *position, uint8_t *finished, int64_t eos,
+                                                 unsigned long long *best, unsigned int *ticket) {
   __shared__ unsigned long long red[kPickThreads / 32];
   __shared__ bool last;
-  pdl_trigger();
-  pdl_wait();
   unsigned long long key = 0ull;
   const int stride = gridDim.x * kPickThreads;
   for (int i = blockIdx.x * kPickThreads + threadIdx.x; i < n; i += stride) {
@@ -311,6 +309,31 @@ pick_commit_kernel(const __nv_bfloat16 *__restrict__ logits, int n, int64_t *nex
       *ticket = 0u;
     }
   }
+}
+
+__global__ void __launch_bounds__(kPickThreads)
+pick_commit_kernel(const __nv_bfloat16 *__restrict__ logits, int n, int64_t *next_token,
+                   int64_t *token, int64_t *position, uint8_t *finished, int64_t eos,
+                   unsigned long long *best, unsigned int *ticket) {
+  pdl_trigger();
+  pdl_wait();
+  pick_commit_body(logits, n, next_token, token, position, finished, eos, best, ticket);
+}
+
+// One pick per sequence in one launch: blockIdx.y is the sequence; its logits row,
+// registers and 16 bytes of scratch are the b-th of each array.
+__global__ void __launch_bounds__(kPickThreads)
+pick_commit_batch_kernel(const __nv_bfloat16 *__restrict__ logits, long long row_stride, int n,
+                         int64_t *next_token, int64_t *token, int64_t *position, uint8_t *finished,
+                         int64_t eos, unsigned long long *scratch) {
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.y;
+  unsigned long long *best = scratch + 2 * b;
+  pick_commit_body(logits + b * row_stride, n, next_token + b, token != nullptr ? token + b : nullptr,
+                   position != nullptr ? position + b : nullptr,
+                   finished != nullptr ? finished + b : nullptr, eos, best,
+                   reinterpret_cast<unsigned int *>(best + 1));
 }
 
 // The same pick when the logits are split over the ranks of a tensor-parallel group
@@ -611,6 +634,27 @@ extern "C" int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_tok
       static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16 *>(logits), n,
       static_cast<int64_t *>(next_token), static_cast<int64_t *>(token),
       static_cast<int64_t *>(position), static_cast<uint8_t *>(finished), eos, best, ticket);
+  return e == cudaSuccess ? kOk : kLaunch;
+}
+
+extern "C" int chr_nf4_pick_commit_batch(const void *logits, int64_t row_stride, int32_t n,
+                                         int32_t batch, void *next_token, void *token,
+                                         void *position, void *finished, int64_t eos,
+                                         void *scratch, void *stream) {
+  if (logits == nullptr || next_token == nullptr || scratch == nullptr) return kNull;
+  if (n < 1 || batch < 1 || batch > 65535 || row_stride < n) return kDims;
+  if (!aligned(scratch, 8)) return kAlign;
+  // a few blocks per sequence: the launch as a whole should cover the SMs once
+  int blocks = (n + kPickThreads * 8 - 1) / (kPickThreads * 8);
+  const int share = (2 * sm_count() + batch - 1) / batch;
+  blocks = blocks < 1 ? 1 : (blocks > share ? share : blocks);
+  const cudaError_t e = launch_chain(
+      pick_commit_batch_kernel, dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(batch)),
+      dim3(kPickThreads), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const __nv_bfloat16 *>(logits), static_cast<long long>(row_stride), n,
+      static_cast<int64_t *>(next_token), static_cast<int64_t *>(token),
+      static_cast<int64_t *>(position), static_cast<uint8_t *>(finished), eos,
+      static_cast<unsigned long long *>(scratch));
   return e == cudaSuccess ? kOk : kLaunch;
 }
 

@@ -8,7 +8,7 @@ registers and its own ``[max_seq, n_kv, head_dim]`` KV block, and the operation
 sequence of a step is the single-sequence one with ``B`` rows: embedding rows ->
 per layer [RMSNorm rows, q/k/v linear, attention of B sequences in one launch,
 o-proj + residual, RMSNorm rows, gate/up linear, SiLU*up, down-proj + residual]
--> final RMSNorm -> lm_head -> one greedy pick + commit per sequence.
+-> final RMSNorm -> lm_head -> greedy pick + commit of all sequences in one launch.
 
 Linears: up to ``GEMV_ROWS`` (4) sequences run through the CUDA-core multi-row GEMV
 (``chr_nf4_gemv_n``: FP32 weights, the numerics of the one-sequence step; one launch
@@ -24,7 +24,7 @@ from collections.abc import Sequence
 import torch
 
 from gpu.nf4 import (ATTN_SPLIT, GEMV_MAX_N, nf4_attn_batch, nf4_gemm_rows, nf4_gemv_n,
-                     nf4_pick_commit, nf4_rms_rows, nf4_silu_mul)
+                     nf4_pick_commit_batch, nf4_rms_rows, nf4_silu_mul)
 
 from .embed import PackedEmbed
 from .graph import capture_on_side_stream
@@ -164,10 +164,8 @@ def batched_forward(state: BatchState, weights: DeviceWeights) -> None:
 def batched_greedy_decode(state: BatchState, weights: DeviceWeights) -> None:
     """Forward for every sequence, then pick + commit per sequence on the device."""
     batched_forward(state, weights)
-    eos = int(state.spec.eos_id)
-    for i in range(state.batch):
-        nf4_pick_commit(state.logits[i], state.next_token[i], state.pick_scratch[i], state.token[i],
-                        state.position[i], state.finished[i], eos)
+    nf4_pick_commit_batch(state.logits, state.next_token, state.pick_scratch, state.token,
+                          state.position, state.finished, int(state.spec.eos_id))
 
 
 class BatchLoop:

@@ -45,6 +45,7 @@ __all__ = [
     "nf4_rope_kv_rows",
     "nf4_silu_mul",
     "nf4_attn_prefill",
+    "nf4_pick_commit_batch",
     "nf4_rope_kv",
     "nf4_set_pdl",
     "nf4_set_tuning",
@@ -752,6 +753,30 @@ def _rows_view(t: torch.Tensor, what: str) -> tuple[int, int]:
     if not t.is_cuda or t.dtype is not torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
         _fail(f"{what} must be a CUDA bfloat16 [N, F] view with contiguous rows")
     return int(t.size(0)), int(t.stride(0))
+
+
+def nf4_pick_commit_batch(logits: torch.Tensor, next_token: torch.Tensor, scratch: torch.Tensor,
+                          token: torch.Tensor | None = None, position: torch.Tensor | None = None,
+                          finished: torch.Tensor | None = None, eos: int = -1) -> None:
+    """Greedy pick + commit for every row of ``logits`` ``[B, n]`` in one launch; per-sequence
+    ``next_token`` / ``token`` / ``position`` (int64 ``[B]``), ``finished`` (uint8 ``[B]``),
+    ``scratch`` uint8 ``[B, 16]`` zeroed once. See ``chr_nf4_pick_commit_batch``."""
+    if not logits.is_cuda or logits.dtype is not torch.bfloat16 or logits.dim() != 2 or logits.stride(1) != 1:
+        _fail("logits must be a CUDA bfloat16 [B, n] view with contiguous rows")
+    b, n = int(logits.size(0)), int(logits.size(1))
+    for t, what, dt in ((next_token, "next_token", torch.int64), (token, "token", torch.int64),
+                        (position, "position", torch.int64), (finished, "finished", torch.uint8)):
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype is not dt or not t.is_contiguous() or t.numel() != b:
+            _fail(f"{what} must be a contiguous CUDA {dt} tensor of {b} elements")
+    if (not scratch.is_cuda or scratch.dtype is not torch.uint8 or not scratch.is_contiguous()
+            or scratch.numel() < 16 * b):
+        _fail("scratch must be contiguous CUDA uint8 with 16 bytes per sequence")
+    rc = _lib.load().chr_nf4_pick_commit_batch(_ptr(logits), int(logits.stride(0)), n, b, _ptr(next_token),
+                                               _ptr(token), _ptr(position), _ptr(finished), int(eos),
+                                               _ptr(scratch), _stream())
+    _lib.check(rc, "chr_nf4_pick_commit_batch")
 
 
 def nf4_pick_commit_tp(

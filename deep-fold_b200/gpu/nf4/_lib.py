@@ -130,6 +130,11 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     ),
+    "chr_nf4_pick_commit_batch": (
+        c_int,
+        [c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+         c_void_p, c_void_p],
+    ),
     "chr_nf4_pick_commit_tp": (
         c_int,
         [c_void_p, c_int32, c_int32, POINTER(ChrNf4Peers), c_void_p, c_void_p, c_void_p, c_void_p,

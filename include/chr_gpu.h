@@ -289,6 +289,16 @@ int chr_nf4_pick_commit(const void *logits, int32_t n, void *next_token,
                         void *token, void *position, void *finished,
                         int64_t eos, void *scratch, void *stream);
 
+/* chr_nf4_pick_commit for B sequences in one launch: logits bf16 [B, n] (rows
+ * row_stride elements apart), next_token / token / position int64 [B], finished
+ * uint8 [B] (token, position, finished optional), scratch B x 16 bytes (8-byte
+ * aligned, zeroed once; every launch leaves it zeroed). Same pick per sequence as the
+ * one-sequence entry (lowest index on ties, NaN above everything). Batched decode is
+ * not in the reference (gpu/decodev2/step.py:182 picks one sequence). */
+int chr_nf4_pick_commit_batch(const void *logits, int64_t row_stride, int32_t n, int32_t batch,
+                              void *next_token, void *token, void *position, void *finished,
+                              int64_t eos, void *scratch, void *stream);
+
 /* chr_nf4_pick_commit when the logits are split over a tensor-parallel group: this rank
  * holds logits_local[0..n_local) = vocabulary ids index_offset..index_offset+n_local-1.
  * Each rank picks its local best, exchanges that one (value, id) pair with every peer
