@@ -1,7 +1,7 @@
 """Microbenchmark of the decode GEMV family on the architectures' real shapes.
 
-    python deep-fold_b200/gpu/nf4/bench_gemv.py [--op gemv|swiglu|qkv] [--shape NAME ...]
-                                                [--iters 40] [--plain]
+    python deep-fold_b200/gpu/nf4/bench_gemv.py [--op gemv|swiglu|qkv|gemv_n] [--shape NAME ...]
+                                                [--rows 4] [--iters 40] [--plain]
 
 Weights are random NF4 blobs; enough distinct copies are rotated through that the
 working set is several times the 126 MB L2 (the reference's microbench rotates
@@ -25,7 +25,7 @@ _PKG = Path(__file__).resolve().parents[2]
 if str(_PKG) not in sys.path:
     sys.path.insert(0, str(_PKG))
 
-from gpu.nf4 import nf4_gemv, nf4_qkv, nf4_swiglu  # noqa: E402
+from gpu.nf4 import nf4_gemv, nf4_gemv_n, nf4_qkv, nf4_swiglu  # noqa: E402
 from gpu.nf4.plan import k_pad  # noqa: E402
 
 SHAPES = {
@@ -83,7 +83,7 @@ def time_launches(fn, n_rot: int, iters: int, plain: bool) -> float:
     return best
 
 
-def run(op: str, name: str, iters: int, plain: bool, gen: torch.Generator) -> dict:
+def run(op: str, name: str, iters: int, plain: bool, gen: torch.Generator, rows: int = 4) -> dict:
     if op == "qkv":
         mq, mkv, k = QKV[name]
         per = nf4_bytes(mq, k) + 2 * nf4_bytes(mkv, k) + k * 2 + (mq + 2 * mkv) * 2
@@ -105,7 +105,15 @@ def run(op: str, name: str, iters: int, plain: bool, gen: torch.Generator) -> di
         mats = [[blob(m, k, gen) for _ in range(n_mats)] for _ in range(n_rot)]
         x = torch.randn(k, device="cuda").to(torch.bfloat16)
         y = torch.empty(m, dtype=torch.bfloat16, device="cuda")
-        if op == "swiglu":
+        if op == "gemv_n":  # the multi-row GEMV: `rows` activation rows through one entry call
+            xr = torch.randn((rows, k), device="cuda").to(torch.bfloat16)
+            yr = torch.empty((rows, m), dtype=torch.bfloat16, device="cuda")
+            per += (rows - 1) * (k * 2 + m * 2)
+
+            def fn(i):
+                (p, s), = mats[i]
+                nf4_gemv_n(p, s, xr, m, k, k_pad(k), out=yr)
+        elif op == "swiglu":
             def fn(i):
                 (gp, gs), (up, us) = mats[i]
                 nf4_swiglu(gp, gs, up, us, x, m, k, k_pad(k), y)
@@ -115,13 +123,17 @@ def run(op: str, name: str, iters: int, plain: bool, gen: torch.Generator) -> di
                 nf4_gemv(p, s, x, m, k, k_pad(k), y)
         shape = [m, k]
     us = time_launches(fn, n_rot, iters, plain)
-    return {"op": op, "shape": name, "MxK": shape, "bytes": per, "us": round(us, 2),
-            "gbs": round(per / us / 1e3, 1), "rotated_copies": n_rot}
+    out = {"op": op, "shape": name, "MxK": shape, "bytes": per, "us": round(us, 2),
+           "gbs": round(per / us / 1e3, 1), "rotated_copies": n_rot}
+    if op == "gemv_n":
+        out["rows"] = rows
+    return out
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemv", choices=("gemv", "swiglu", "qkv"))
+    ap.add_argument("--op", default="gemv", choices=("gemv", "swiglu", "qkv", "gemv_n"))
+    ap.add_argument("--rows", type=int, default=4, help="activation rows of --op gemv_n (1..8)")
     ap.add_argument("--shape", nargs="*", default=None)
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--plain", action="store_true")
@@ -129,9 +141,9 @@ def main() -> None:
     gen = torch.Generator(device="cuda")
     gen.manual_seed(0)
     names = args.shape or (list(QKV) if args.op == "qkv" else
-                           [n for n in SHAPES if args.op == "gemv" or "gate" in n])
+                           [n for n in SHAPES if args.op in ("gemv", "gemv_n") or "gate" in n])
     for name in names:
-        print(json.dumps(run(args.op, name, args.iters, args.plain, gen)), flush=True)
+        print(json.dumps(run(args.op, name, args.iters, args.plain, gen, args.rows)), flush=True)
         torch.cuda.empty_cache()
 
 
