@@ -453,6 +453,7 @@ def run_ours(args, spec) -> None:
                      ", sustained (back-to-back launches inside a long sweep)",
                      "peak_burst": peaks["tf_burst"], "unit": "TFLOP/s",
                      "frac": tf / peaks["tf_sustained"], "frac_of_burst": tf / peaks["tf_burst"],
+                     "frac_of_nominal_2250": tf / 2250.0,
                      "shape": [gu[0].M, gu[0].K, n_tok], "us_per_launch": g_ms * 1e3, "traffic": None}
         del xin, yout
 

@@ -8,8 +8,8 @@
 // Why the rows are nearly free. The one-row kernel is bound by its 8-byte table
 // lookups (two shared-memory wavefronts per 64 weights). Here a lookup feeds four
 // packed FMAs instead of one, and the x pairs are unpacked from bf16 once per code
-// word for both weight rows a warp carries: about 5 instructions per weight for four
-// rows against 2.7 for one.
+// word for both weight rows a warp carries: about 6 instructions per weight for four
+// rows against 2.7 for one (measured).
 //
 // Work split (as in gemv_ring.cuh, simplified to one matrix): a CTA of S*G working
 // warps and one helper warp; a warp owns one 1024-wide chunk of K (S chunks per CTA,
