@@ -195,3 +195,41 @@ def test_the_reference_binding_compiles_against_this_header(tmp_path):
         cmd.append(f"-I{cuda_inc}")
     res = subprocess.run(cmd + [str(src)], capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-3000:]
+
+
+def test_workspace_queries_of_the_wide_gemm_and_the_multi_row_gemv():
+    """Host-only arithmetic behind ``chr_nf4_gemm_rows_ws`` and ``chr_nf4_gemv_n_ws`` (no launch;
+    without a GPU the planners assume 148 SMs). Split-K is taken where the tile grid alone
+    leaves SMs idle and a cut does not just add a second wave; the workspace is
+    ``splits * M * N`` floats."""
+    from gpu.nf4 import _lib
+    from gpu.nf4._lib import ChrNf4Dev
+
+    lib = _lib.load()
+
+    def gemm_ws(m, k, n):
+        return int(lib.chr_nf4_gemm_rows_ws(ctypes.byref(ChrNf4Dev(m, k, k, 1, 1)), n))
+
+    # stacked 32B gate/up: 432 row tiles fill the device, no split at any N
+    for n in (16, 512, 4096):
+        assert gemm_ws(55296, 5120, n) == 0
+    # 32B down-proj at the chunk width: 80 CTAs on 148 SMs -> cut K, but not in two
+    # (160 CTAs would be two waves of half the work each)
+    ws = gemm_ws(5120, 27648, 512)
+    assert ws > 0 and ws % (5120 * 512) == 0
+    splits = ws // (5120 * 512)
+    assert 3 <= splits <= 16
+    # a short K is not worth a reduction pass at wide N
+    assert gemm_ws(5120, 5120, 512) == 0
+    # one decode-sized row block of a long-K matrix: many splits, each at least 8 K tiles
+    ws16 = gemm_ws(5120, 27648, 16)
+    assert ws16 % (5120 * 16) == 0 and 4 <= ws16 // (5120 * 16) <= 16
+
+    def gemv_n_ws(m, k, n):
+        return int(lib.chr_nf4_gemv_n_ws(ctypes.byref(ChrNf4Dev(m, k, k, 1, 1)), n))
+
+    assert gemv_n_ws(2048, 5120, 4) == 0               # 5 chunks of 1024: one K slice
+    assert gemv_n_ws(2048, 11264, 8) == 0              # 11 chunks: still one
+    assert gemv_n_ws(64, 27648, 8) == 3 * 4 * 64       # 27 chunks -> 3 slices, 4 rows per pass
+    assert gemv_n_ws(64, 27648, 3) == 3 * 3 * 64
+    assert gemv_n_ws(64, 27648, 9) == 0                # more than 8 rows: refused (no workspace)
